@@ -1,4 +1,5 @@
 from .model_config import ConfigError, LlamaConfig, RopeScaling, read_config_json
 from .engine_config import EngineConfig
+from .viresun_config import ViresunConfig
 
-__all__ = ["ConfigError", "LlamaConfig", "RopeScaling", "read_config_json", "EngineConfig"]
+__all__ = ["ConfigError", "LlamaConfig", "RopeScaling", "read_config_json", "EngineConfig", "ViresunConfig"]

@@ -1,0 +1,274 @@
+// Grouped-query attention whose scores carry a bias that depends on the distance between
+// query and key, over a paged cache in which a token keeps its key and its value side by
+// side (so keys and values may differ in size), behind an optional sliding window:
+//
+//   score(i, j) = (q_i . k_j) * scale - r1[h] * ln(1 + r2[h] * (i - j))       for 0 <= i - j < window
+//   out_i       = softmax_j(score(i, .)) . v
+//
+// and the kernel that prepares its operands: every query and key head divided by its root
+// mean square (no weight), queries multiplied by 1 + coef * ln(floor((pos + 1) / every) + 1),
+// keys and values written into the page and slot of their position.
+//
+//   q, out : [T, nh, D] and [T, nh, VD]
+//   cache  : one run's pages, [page][nkv][P][D + VD]
+//   block_table : [nseq, max_blocks] page ids; entries the window has passed are never read
+//
+// Scores, softmax, bias and the weighted sum are 32-bit whatever the storage type.  Head
+// sizes are run-time values (any D, VD up to 256), so these kernels live in the core library.
+// The step's rows are found through seq_start alone: a grid planned from the number of
+// rows and sequences serves whatever lengths the sequences have.
+#include "common.cuh"
+#include <float.h>
+
+#define QKN_THREADS 128
+#define MAX_HEAD 256
+
+// one warp per (row, head) of the stacked projection [q heads | k heads | v heads]
+template <typename TI, typename TA>
+__global__ void __launch_bounds__(QKN_THREADS)
+qk_norm_store_kernel(const TI* __restrict__ in, long long ld_in, TA* __restrict__ q_out, TA* __restrict__ cache,
+                     const int* __restrict__ positions, const int* __restrict__ token_seq,
+                     const int* __restrict__ block_table, int max_blocks, int T, int nh, int nkv, int D, int VD, int P,
+                     size_t page_stride, float eps, int normalise, float temp_coef, int temp_every) {
+    const int lane = threadIdx.x & 31;
+    const long long unit = (long long)blockIdx.x * (QKN_THREADS / 32) + (threadIdx.x >> 5);
+    const int heads = nh + 2 * nkv;
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    if (unit >= (long long)T * heads) return;
+    const int t = (int)(unit / heads), hh = (int)(unit % heads);
+    const int pos = positions[t];
+    const TI* row = in + (size_t)t * ld_in;
+    if (hh < nh + nkv) {
+        const bool is_q = hh < nh;
+        const TI* src = row + (is_q ? (size_t)hh * D : (size_t)nh * D + (size_t)(hh - nh) * D);
+        float v[MAX_HEAD / 32];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAX_HEAD / 32; ++i) {
+            const int d = lane + 32 * i;
+            v[i] = d < D ? ap_to_float(src[d]) : 0.f;
+            ss = fmaf(v[i], v[i], ss);
+        }
+        ss = ap_warp_sum(ss);
+        float f = normalise ? 1.0f / sqrtf(ss / (float)D + eps) : 1.0f;
+        if (is_q && temp_every > 0) f *= 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f);
+        TA* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)t * nh + hh) * D;
+        } else {
+            if (cache == nullptr) return;
+            const int page = block_table[(size_t)token_seq[t] * max_blocks + pos / P];
+            dst = cache + (size_t)page * page_stride + ((size_t)(hh - nh) * P + pos % P) * (D + VD);
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_HEAD / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < D) dst[d] = ap_from_float<TA>(v[i] * f);
+        }
+    } else {
+        if (cache == nullptr) return;
+        const int g = hh - nh - nkv;
+        const TI* src = row + (size_t)(nh + nkv) * D + (size_t)g * VD;
+        const int page = block_table[(size_t)token_seq[t] * max_blocks + pos / P];
+        TA* dst = cache + (size_t)page * page_stride + ((size_t)g * P + pos % P) * (D + VD) + D;
+        for (int d = lane; d < VD; d += 32) dst[d] = ap_from_float<TA>(ap_to_float(src[d]));
+    }
+}
+
+AP_EXPORT int ap_qk_norm_store(const void* in, int in_dtype, long long ld_in, void* q_out, void* cache, int act_dtype,
+                               const int* positions, const int* token_seq, const int* block_table, int max_blocks,
+                               int T, int nh, int nkv, int D, int VD, int P, long long page_stride, float eps,
+                               int normalise, float temp_coef, int temp_every, cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && D > 0 && VD > 0 && D <= MAX_HEAD && VD <= MAX_HEAD,
+               "qk_norm_store: bad sizes T=%d heads=%d/%d sizes %d/%d (at most %d)", T, nh, nkv, D, VD, MAX_HEAD);
+    AP_REQUIRE(cache == nullptr || (token_seq && block_table && max_blocks > 0 && P > 0),
+               "qk_norm_store: storing needs token_seq and a block table");
+    AP_REQUIRE(temp_every >= 0, "qk_norm_store: the temperature's period must not be negative");
+    if (T == 0) return AP_OK;
+    const long long units = (long long)T * (nh + 2 * nkv);
+    const dim3 grid((unsigned)((units + QKN_THREADS / 32 - 1) / (QKN_THREADS / 32)));
+#define LAUNCH(TI, TA)                                                                                              \
+    AP_CHECK_PDL_LAUNCH("qk_norm_store",                                                                            \
+                        ap_launch_pdl(qk_norm_store_kernel<TI, TA>, grid, dim3(QKN_THREADS), 0, stream, (const TI*)in, \
+                                      ld_in, (TA*)q_out, (TA*)cache, positions, token_seq, block_table, max_blocks, T, \
+                                      nh, nkv, D, VD, P, (size_t)page_stride, eps, normalise, temp_coef, temp_every))
+    if (in_dtype == AP_F32 && act_dtype == AP_F32) LAUNCH(float, float);
+    else if (in_dtype == AP_F32 && act_dtype == AP_BF16) LAUNCH(float, bf16);
+    else if (in_dtype == AP_BF16 && act_dtype == AP_BF16) LAUNCH(bf16, bf16);
+    else AP_REQUIRE(false, "qk_norm_store: unsupported dtypes in=%d act=%d", in_dtype, act_dtype);
+#undef LAUNCH
+    return AP_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// The attention itself.  A CTA of four warps takes up to QT consecutive rows of one
+// sequence and one query head; keys come in tiles of KT (one key per lane), with their
+// values, through shared memory; every warp owns up to RPW rows, runs their online softmax
+// and holds their output in registers (lane c of VD / 32 columns).
+// ---------------------------------------------------------------------------------------
+#define AWB_THREADS 128
+#define AWB_WARPS 4
+#define RPW 4
+#define QT (AWB_WARPS * RPW)
+#define KT 32
+
+template <typename TA>
+__global__ void __launch_bounds__(AWB_THREADS)
+attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, const TA* __restrict__ cache,
+                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_start,
+                             const int* __restrict__ positions, int nseq, int nh, int nkv, int D, int VD, int P,
+                             size_t page_stride, float scale, int window, const float* __restrict__ r1,
+                             const float* __restrict__ r2) {
+    extern __shared__ __align__(16) float smem[];
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    // which sequence and which of its row tiles this CTA serves
+    int b = blockIdx.x, seq = -1, row0 = 0, nrows = 0;
+    for (int s = 0; s < nseq; ++s) {
+        const int a = seq_start[s], n = seq_start[s + 1] - a;
+        const int tiles = (n + QT - 1) / QT;
+        if (b < tiles) {
+            seq = s;
+            row0 = a + b * QT;
+            nrows = min(QT, n - b * QT);
+            break;
+        }
+        b -= tiles;
+    }
+    if (seq < 0) return;
+    const int h = blockIdx.y, kvh = h / (nh / nkv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int DP = D + 1;
+    float* q_s = smem;                        // [QT][D]
+    float* k_s = q_s + QT * D;                // [KT][D + 1]
+    float* v_s = k_s + KT * DP;               // [KT][VD]
+    float* p_s = v_s + KT * VD;               // [AWB_WARPS][RPW][KT]
+    const int* table = block_table + (size_t)seq * max_blocks;
+    const int pos_first = positions[row0], pos_last = pos_first + nrows - 1;
+    for (int i = threadIdx.x; i < nrows * D; i += AWB_THREADS) {
+        const int r = i / D, d = i - r * D;
+        q_s[r * D + d] = ap_to_float(q[((size_t)(row0 + r) * nh + h) * D + d]);
+    }
+    const float b1 = r1 ? r1[h] : 0.f, b2 = r2 ? r2[h] : 0.f;
+    const int klo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    constexpr int NC = MAX_HEAD / 32;
+    float acc[RPW][NC];
+    float m[RPW], l[RPW];
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+        m[i] = -FLT_MAX;
+        l[i] = 0.f;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[i][c] = 0.f;
+    }
+    const int nc = (VD + 31) / 32;
+    const int my_rows = min(RPW, nrows - warp * RPW);        // <= 0: this warp only helps loading
+    for (int k0 = klo; k0 <= pos_last; k0 += KT) {
+        __syncthreads();                                     // the tile before is consumed (and q_s is written)
+        for (int j = warp; j < KT; j += AWB_WARPS) {
+            const int kp = k0 + j;
+            if (kp <= pos_last) {
+                const int page = table[kp / P];
+                const TA* src = cache + (size_t)page * page_stride + ((size_t)kvh * P + kp % P) * (D + VD);
+                for (int d = lane; d < D; d += 32) k_s[j * DP + d] = ap_to_float(src[d]);
+                for (int d = lane; d < VD; d += 32) v_s[j * VD + d] = ap_to_float(src[D + d]);
+            } else {
+                for (int d = lane; d < D; d += 32) k_s[j * DP + d] = 0.f;
+                for (int d = lane; d < VD; d += 32) v_s[j * VD + d] = 0.f;
+            }
+        }
+        __syncthreads();
+        if (my_rows <= 0) continue;
+        // scores of key `lane` for this warp's rows
+        float s[RPW];
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) s[i] = 0.f;
+        const float* kr = k_s + lane * DP;
+        const float* qr = q_s + (warp * RPW) * D;
+        for (int d = 0; d < D; ++d) {
+            const float kv = kr[d];
+#pragma unroll
+            for (int i = 0; i < RPW; ++i) s[i] = fmaf(qr[i * D + d], kv, s[i]);   // rows past the tile read finite junk
+        }
+        const int kp = k0 + lane;
+        float* pw = p_s + warp * RPW * KT;
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) {
+            const int qpos = pos_first + warp * RPW + i;
+            const int dist = qpos - kp;
+            const bool seen = i < my_rows && dist >= 0 && (window <= 0 || dist < window);
+            float sc = -FLT_MAX;
+            if (seen) sc = s[i] * scale - b1 * log1pf(b2 * (float)dist);
+            const float m_new = fmaxf(m[i], ap_warp_max(sc));
+            const float p = seen ? expf(sc - m_new) : 0.f;
+            const float alpha = expf(m[i] - m_new);
+            l[i] = l[i] * alpha + ap_warp_sum(p);
+            m[i] = m_new;
+            pw[i * KT + lane] = p;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) acc[i][c] *= alpha;
+        }
+        __syncwarp();
+        for (int j = 0; j < KT; ++j) {
+            float pj[RPW];
+#pragma unroll
+            for (int i = 0; i < RPW; ++i) pj[i] = pw[i * KT + j];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                if (c < nc) {
+                    const int d = lane + 32 * c;
+                    const float vv = d < VD ? v_s[j * VD + d] : 0.f;
+#pragma unroll
+                    for (int i = 0; i < RPW; ++i) acc[i][c] = fmaf(pj[i], vv, acc[i][c]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+        if (i < my_rows) {
+            const float inv = 1.0f / l[i];
+            TA* o = out + ((size_t)(row0 + warp * RPW + i) * nh + h) * VD;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const int d = lane + 32 * c;
+                if (d < VD) o[d] = ap_from_float<TA>(acc[i][c] * inv);
+            }
+        }
+    }
+}
+
+AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cache, int dtype, const int* block_table,
+                                       int max_blocks, const int* seq_start, const int* positions, int nseq, int T,
+                                       int nh, int nkv, int D, int VD, int P, long long page_stride, float scale,
+                                       int window, const float* r1, const float* r2, cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && nseq >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0 && P > 0 && max_blocks > 0,
+               "attention_window_bias: bad sizes T=%d heads=%d kv_heads=%d page=%d", T, nh, nkv, P);
+    AP_REQUIRE(D > 0 && VD > 0 && D <= MAX_HEAD && VD <= MAX_HEAD,
+               "attention_window_bias: head sizes %d/%d are not in 1..%d", D, VD, MAX_HEAD);
+    AP_REQUIRE(nh <= 65535, "attention_window_bias: %d heads exceed the grid", nh);
+    AP_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attention_window_bias: the bias needs both of its tables");
+    if (T == 0 || nseq == 0) return AP_OK;
+    // every sequence's rows in tiles of QT: at most T / QT whole tiles and one ragged tile per sequence
+    const dim3 grid((unsigned)(T / QT + nseq), (unsigned)nh);
+    const size_t smem = ((size_t)QT * D + (size_t)KT * (D + 1) + (size_t)KT * VD + AWB_WARPS * RPW * KT) * sizeof(float);
+#define LAUNCH(TA)                                                                                                   \
+    do {                                                                                                             \
+        auto kern = attention_window_bias_kernel<TA>;                                                                \
+        if (smem > 48 * 1024) {                                                                                      \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+            AP_REQUIRE(e == cudaSuccess, "attention_window_bias: cannot reserve %zu bytes of shared memory", smem);  \
+        }                                                                                                            \
+        AP_CHECK_PDL_LAUNCH("attention_window_bias",                                                                 \
+                            ap_launch_pdl(kern, grid, dim3(AWB_THREADS), smem, stream, (const TA*)q, (TA*)out,       \
+                                          (const TA*)cache, block_table, max_blocks, seq_start, positions, nseq, nh, \
+                                          nkv, D, VD, P, (size_t)page_stride, scale, window, r1, r2));               \
+    } while (0)
+    if (dtype == AP_F32) LAUNCH(float);
+    else if (dtype == AP_BF16) LAUNCH(bf16);
+    else AP_REQUIRE(false, "attention_window_bias: unknown dtype %d", dtype);
+#undef LAUNCH
+    return AP_OK;
+}

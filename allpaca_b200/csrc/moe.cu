@@ -1,0 +1,327 @@
+// A routed feed-forward (mixture of experts) and the gated activations of feed-forwards:
+//
+//   moe_route      per row: the `top` experts with the largest router logits (ties: the lower
+//                  index), weights = softmax over the chosen logits; all 32-bit
+//   moe_sort       (row, choice) pairs grouped by expert: a permutation, every pair's place in
+//                  it, and a list of row tiles (expert, first place, rows) for the products
+//   moe_gate_up    for every tile: y = act(A W_gate[e]^T, A W_up[e]^T), rows gathered by the permutation
+//   moe_down       for every tile: o = y W_down[e]^T, 32-bit
+//   moe_combine    delta[t] = sum_k weight[t,k] * o[place(t,k)], in the order of k
+//   gated_act      the activation alone, for a dense feed-forward whose product left [gate | up]
+//
+// Activations (g = gate, u = up):
+//   0 silu:   g / (1 + exp(-g)) * u
+//   1 relu:   max(g, 0) * u
+//   2 clamped sigmoid gate: g' = min(g, limit), u' = clamp(u, -limit, limit); g' * sigmoid(alpha g') * (u' + shift)
+//
+// The products run on the CUDA cores with 32-bit accumulation (every output element one
+// thread's sum over k in ascending order), so a row's result does not depend on where the
+// sort placed it or on what else is in the batch.  Nothing is decided on the host: counts and
+// tiles stay on the device, grids are planned for the worst case and surplus CTAs return.
+#include "common.cuh"
+#include <float.h>
+
+#define ACT_SILU 0
+#define ACT_RELU 1
+#define ACT_CLAMPED 2
+
+__device__ __forceinline__ float gated_activation(float g, float u, int act, float limit, float alpha, float shift) {
+    if (act == ACT_RELU) return fmaxf(g, 0.f) * u;
+    if (act == ACT_CLAMPED) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-alpha * g)) * (u + shift);
+    }
+    return g / (1.0f + expf(-g)) * u;
+}
+
+// ---- the activation alone ------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void gated_act_kernel(const TI* __restrict__ in, TO* __restrict__ out, int T, int I, int pairs, int act,
+                                 float limit, float alpha, float shift) {
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    const size_t n = (size_t)T * I;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / I, j = e - t * I;
+        const size_t base = t * 2 * (size_t)I;
+        const float g = ap_to_float(in[pairs ? base + 2 * j : base + j]);
+        const float u = ap_to_float(in[pairs ? base + 2 * j + 1 : base + I + j]);
+        out[e] = ap_from_float<TO>(gated_activation(g, u, act, limit, alpha, shift));
+    }
+}
+
+AP_EXPORT int ap_gated_act(const void* in, int in_dtype, void* out, int out_dtype, int T, int I, int pairs, int act,
+                           float limit, float alpha, float shift, cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && I > 0 && act >= 0 && act <= 2, "gated_act: bad sizes T=%d I=%d or activation %d", T, I, act);
+    if (T == 0) return AP_OK;
+    long long blocks = ((long long)T * I + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+#define LAUNCH(TI, TO)                                                                                              \
+    AP_CHECK_PDL_LAUNCH("gated_act", ap_launch_pdl(gated_act_kernel<TI, TO>, dim3((unsigned)blocks), dim3(256), 0, stream, \
+                                                   (const TI*)in, (TO*)out, T, I, pairs, act, limit, alpha, shift))
+    if (in_dtype == AP_F32 && out_dtype == AP_F32) LAUNCH(float, float);
+    else if (in_dtype == AP_F32 && out_dtype == AP_BF16) LAUNCH(float, bf16);
+    else if (in_dtype == AP_BF16 && out_dtype == AP_BF16) LAUNCH(bf16, bf16);
+    else AP_REQUIRE(false, "gated_act: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+#undef LAUNCH
+    return AP_OK;
+}
+
+// ---- routing ---------------------------------------------------------------------------
+#define ROUTE_MAX_PER_LANE 8          // experts <= 256
+#define ROUTE_MAX_TOP 16
+
+// one warp per row; logits: [T, E] 32-bit (bias not yet added)
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ chosen,
+                 float* __restrict__ weight, int T, int E, int top) {
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    float z[ROUTE_MAX_PER_LANE];
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        z[i] = e < E ? logits[(size_t)t * E + e] + (bias ? bias[e] : 0.f) : -FLT_MAX;
+    }
+    float best[ROUTE_MAX_TOP];
+    int who[ROUTE_MAX_TOP];
+    for (int k = 0; k < top; ++k) {
+        float v = -FLT_MAX;
+        int idx = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E && (z[i] > v || (z[i] == v && e < idx))) { v = z[i]; idx = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+        }
+        best[k] = v;
+        who[k] = idx;
+#pragma unroll
+        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
+            if (lane + 32 * i == idx) z[i] = -FLT_MAX;        // taken
+    }
+    if (lane == 0) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) sum += expf(best[k] - best[0]);      // best[0] is the largest
+        for (int k = 0; k < top; ++k) {
+            chosen[(size_t)t * top + k] = who[k];
+            weight[(size_t)t * top + k] = expf(best[k] - best[0]) / sum;
+        }
+    }
+}
+
+AP_EXPORT int ap_moe_route(const float* logits, const float* bias, int* chosen, float* weight, int T, int E, int top,
+                           cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && E > 0 && E <= 32 * ROUTE_MAX_PER_LANE && top > 0 && top <= E && top <= ROUTE_MAX_TOP,
+               "moe_route: %d experts (at most %d), %d chosen (at most %d)", E, 32 * ROUTE_MAX_PER_LANE, top, ROUTE_MAX_TOP);
+    if (T == 0) return AP_OK;
+    AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel, dim3((unsigned)((T + 3) / 4)), dim3(128), 0, stream,
+                                                   logits, bias, chosen, weight, T, E, top));
+    return AP_OK;
+}
+
+// ---- grouping pairs by expert ------------------------------------------------------------
+#define MOE_BM 64
+#define MOE_BN 64
+#define MOE_BK 16
+#define SORT_MAX_EXPERTS 256
+
+// One CTA.  place[pair] = position of the pair in the grouped order; perm[position] = pair;
+// tiles[i] = (expert, first position, rows); tiles[max_tiles] holds their number in .x.
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ chosen, int* __restrict__ perm, int* __restrict__ place, int3* __restrict__ tiles,
+                int pairs, int E, int max_tiles) {
+    __shared__ int count[SORT_MAX_EXPERTS];
+    __shared__ int first[SORT_MAX_EXPERTS + 1];
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&count[chosen[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, nt = 0;
+        for (int e = 0; e < E; ++e) {
+            first[e] = at;
+            for (int r = 0; r < count[e] && nt < max_tiles; r += MOE_BM) tiles[nt++] = make_int3(e, at + r, min(MOE_BM, count[e] - r));
+            at += count[e];
+        }
+        first[E] = at;
+        tiles[max_tiles] = make_int3(nt, 0, 0);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = chosen[i];
+        const int p = first[e] + atomicAdd(&count[e], 1);
+        perm[p] = i;
+        place[i] = p;
+    }
+}
+
+AP_EXPORT int ap_moe_max_tiles(int pairs, int E) { return (pairs + MOE_BM - 1) / MOE_BM + E; }
+
+AP_EXPORT int ap_moe_sort(const int* chosen, int* perm, int* place, int* tiles, int pairs, int E, cudaStream_t stream) {
+    AP_REQUIRE(pairs >= 0 && E > 0 && E <= SORT_MAX_EXPERTS, "moe_sort: %d experts (at most %d)", E, SORT_MAX_EXPERTS);
+    if (pairs == 0) return AP_OK;
+    AP_CHECK_PDL_LAUNCH("moe_sort", ap_launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, chosen, perm, place,
+                                                  (int3*)tiles, pairs, E, ap_moe_max_tiles(pairs, E)));
+    return AP_OK;
+}
+
+// ---- the experts' products ---------------------------------------------------------------
+// GATED: the weight of expert e is [2 F, K] (gate rows, then up rows); out[p, f] = act(gate, up).
+// else : the weight is [N, K]; out[p, n] 32-bit.
+// A rows: GATED gathers a[perm[p] / top]; else a[p].
+template <typename TA, typename TW, typename TO, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, long long w_expert_stride,
+                TO* __restrict__ C, long long ldc, const int* __restrict__ perm, int top, const int3* __restrict__ tiles,
+                int max_tiles, int N, int K, int act, float limit, float alpha, float shift) {
+    __shared__ float As[MOE_BK][MOE_BM + 4];
+    __shared__ float Ws[GATED ? 2 : 1][MOE_BK][MOE_BN + 4];
+    __shared__ int src_row[MOE_BM];
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    if ((int)blockIdx.y >= tiles[max_tiles].x) return;
+    const int3 tile = tiles[blockIdx.y];
+    const int e = tile.x, p0 = tile.y, rows = tile.z;
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int n0 = blockIdx.x * MOE_BN;
+    const TW* We = W + (size_t)e * w_expert_stride;
+    if (tid < MOE_BM) src_row[tid] = tid < rows ? (GATED ? perm[p0 + tid] / top : p0 + tid) : -1;
+    __syncthreads();
+    float acc[4][4], acc2[GATED ? 4 : 1][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            acc[i][j] = 0.f;
+            if constexpr (GATED) acc2[i][j] = 0.f;
+        }
+    const int lrow = tid >> 2, lk = (tid & 3) * 4;
+    const int arow = src_row[lrow];
+    for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int k = k0 + lk + q;
+            const int wn = n0 + lrow;
+            As[lk + q][lrow] = (arow >= 0 && k < K) ? ap_to_float(A[(size_t)arow * lda + k]) : 0.f;
+            Ws[0][lk + q][lrow] = (wn < N && k < K) ? ap_to_float(We[(size_t)wn * K + k]) : 0.f;
+            if constexpr (GATED) Ws[1][lk + q][lrow] = (wn < N && k < K) ? ap_to_float(We[(size_t)(N + wn) * K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MOE_BK; ++kk) {
+            float a[4], w[4], w2[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                w[j] = Ws[0][kk][tx * 4 + j];
+                if constexpr (GATED) w2[j] = Ws[1][kk][tx * 4 + j];
+                else w2[j] = 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+                    if constexpr (GATED) acc2[i][j] = fmaf(a[i], w2[j], acc2[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if constexpr (GATED) v = gated_activation(acc[i][j], acc2[i][j], act, limit, alpha, shift);
+            C[(size_t)(p0 + r) * ldc + n] = ap_from_float<TO>(v);
+        }
+    }
+}
+
+// a: [T, K]; w_gate_up: [E, 2 F, K]; y: [pairs, F] in the activation type
+AP_EXPORT int ap_moe_gate_up(const void* a, int a_dtype, const void* w, int w_dtype, void* y, int y_dtype,
+                             const int* perm, int top, const int* tiles, int pairs, int E, int F, int K, int act,
+                             float limit, float alpha, float shift, cudaStream_t stream) {
+    AP_REQUIRE(pairs >= 0 && E > 0 && F > 0 && K > 0 && top > 0 && act >= 0 && act <= 2, "moe_gate_up: bad sizes");
+    if (pairs == 0) return AP_OK;
+    const int max_tiles = ap_moe_max_tiles(pairs, E);
+    const dim3 grid((unsigned)((F + MOE_BN - 1) / MOE_BN), (unsigned)max_tiles);
+    AP_REQUIRE(max_tiles <= 65535, "moe_gate_up: %d row tiles exceed the grid", max_tiles);
+#define LAUNCH(TA, TW, TO)                                                                                           \
+    AP_CHECK_PDL_LAUNCH("moe_gate_up", ap_launch_pdl(moe_gemm_kernel<TA, TW, TO, true>, grid, dim3(256), 0, stream,  \
+                                                     (const TA*)a, (long long)K, (const TW*)w, (long long)2 * F * K, \
+                                                     (TO*)y, (long long)F, perm, top, (const int3*)tiles, max_tiles, F, K, \
+                                                     act, limit, alpha, shift))
+    if (a_dtype == AP_F32 && w_dtype == AP_F32 && y_dtype == AP_F32) LAUNCH(float, float, float);
+    else if (a_dtype == AP_BF16 && w_dtype == AP_BF16 && y_dtype == AP_BF16) LAUNCH(bf16, bf16, bf16);
+    else if (a_dtype == AP_BF16 && w_dtype == AP_F32 && y_dtype == AP_BF16) LAUNCH(bf16, float, bf16);
+    else AP_REQUIRE(false, "moe_gate_up: unsupported dtypes a=%d w=%d y=%d", a_dtype, w_dtype, y_dtype);
+#undef LAUNCH
+    return AP_OK;
+}
+
+// y: [pairs, F]; w_down: [E, H, F]; o: [pairs, H] 32-bit
+AP_EXPORT int ap_moe_down(const void* y, int y_dtype, const void* w, int w_dtype, float* o, const int* tiles, int pairs,
+                          int E, int H, int F, cudaStream_t stream) {
+    AP_REQUIRE(pairs >= 0 && E > 0 && F > 0 && H > 0, "moe_down: bad sizes");
+    if (pairs == 0) return AP_OK;
+    const int max_tiles = ap_moe_max_tiles(pairs, E);
+    const dim3 grid((unsigned)((H + MOE_BN - 1) / MOE_BN), (unsigned)max_tiles);
+    AP_REQUIRE(max_tiles <= 65535, "moe_down: %d row tiles exceed the grid", max_tiles);
+#define LAUNCH(TA, TW)                                                                                               \
+    AP_CHECK_PDL_LAUNCH("moe_down", ap_launch_pdl(moe_gemm_kernel<TA, TW, float, false>, grid, dim3(256), 0, stream, \
+                                                  (const TA*)y, (long long)F, (const TW*)w, (long long)H * F, o,     \
+                                                  (long long)H, (const int*)nullptr, 1, (const int3*)tiles, max_tiles, H, \
+                                                  F, 0, 0.f, 0.f, 0.f))
+    if (y_dtype == AP_F32 && w_dtype == AP_F32) LAUNCH(float, float);
+    else if (y_dtype == AP_BF16 && w_dtype == AP_BF16) LAUNCH(bf16, bf16);
+    else if (y_dtype == AP_BF16 && w_dtype == AP_F32) LAUNCH(bf16, float);
+    else AP_REQUIRE(false, "moe_down: unsupported dtypes y=%d w=%d", y_dtype, w_dtype);
+#undef LAUNCH
+    return AP_OK;
+}
+
+// delta[t, :] = sum_k weight[t, k] * o[place[t * top + k], :]
+__global__ void moe_combine_kernel(const float* __restrict__ o, const int* __restrict__ place,
+                                   const float* __restrict__ weight, float* __restrict__ delta, int T, int H, int top) {
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    const size_t n = (size_t)T * H;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / H, c = e - t * H;
+        float v = 0.f;
+        for (int k = 0; k < top; ++k)
+            v = fmaf(weight[t * top + k], o[(size_t)place[t * top + k] * H + c], v);
+        delta[e] = v;
+    }
+}
+
+AP_EXPORT int ap_moe_combine(const float* o, const int* place, const float* weight, float* delta, int T, int H, int top,
+                             cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && H > 0 && top > 0, "moe_combine: bad sizes");
+    if (T == 0) return AP_OK;
+    long long blocks = ((long long)T * H + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    AP_CHECK_PDL_LAUNCH("moe_combine", ap_launch_pdl(moe_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, o,
+                                                     place, weight, delta, T, H, top));
+    return AP_OK;
+}

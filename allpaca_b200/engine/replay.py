@@ -55,6 +55,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                        max_num_batched_tokens=max(rounded, args.max_live), prefill_chunk=rounded,
                        use_cuda_graphs=not args.no_graphs)
     runner = ModelRunner(args.model, cfg)
+    # a request never holds more than the pool: block tables need not be wider than that
+    runner.max_model_len = min(runner.max_model_len, rounded)
     for line in sys.stdin:
         line = line.strip()
         if not line:

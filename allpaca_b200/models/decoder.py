@@ -36,6 +36,8 @@ class DecoderModel:
         self.env = env
         self.blocks: List[Block] = [build("block", b, env) for b in spec.layers]
         self.final_norm = build("norm", spec.final_norm, env)
+        self.embedding_norm = build("norm", spec.embedding_norm, env) if spec.embedding_norm is not None else None
+        self._sinusoid_inv_freq: Optional[torch.Tensor] = None
         self.embedding: Optional[torch.Tensor] = None
         self.head = Linear(env, spec.vocab_size, spec.hidden_size)
         self.head_bias: Optional[torch.Tensor] = None
@@ -64,6 +66,9 @@ class DecoderModel:
             out[s.head_bias_name] = (WeightSpec((s.vocab_size,), "bias"), None, "head_bias")
         for name, ws in self.final_norm.weights().items():
             out[s.final_norm_prefix + name] = (ws, self.final_norm, name)
+        if self.embedding_norm is not None:
+            for name, ws in self.embedding_norm.weights().items():
+                out[s.embedding_norm_prefix + name] = (ws, self.embedding_norm, name)
         for block, prefix in zip(self.blocks, s.layer_prefixes):
             for sub_prefix, part in block.sub_parts().items():
                 for name, ws in part.weights().items():
@@ -114,6 +119,8 @@ class DecoderModel:
         """Whether any part decides on the host, step by step, what it launches (such a model's
         steps are not recorded as CUDA graphs)."""
         every = [p for b in self.blocks for p in b.parts()] + list(self.final_norm.parts())
+        if self.embedding_norm is not None:
+            every += list(self.embedding_norm.parts())
         return any(p.host_control for p in every)
 
     def state_bytes(self) -> List[int]:
@@ -139,6 +146,18 @@ class DecoderModel:
                 cache.group = g
             self.caches[r] = cache
 
+    def _sinusoid_frequencies(self) -> Optional[torch.Tensor]:
+        """``base^(-2i/width)`` for every pair of entries: formed in 64-bit, rounded to 32-bit once."""
+        s = self.spec
+        if s.embedding_sinusoid_base is None:
+            return None
+        if self._sinusoid_inv_freq is None:
+            i = torch.arange(s.hidden_size // 2, dtype=torch.float64)
+            freq = torch.pow(torch.tensor(float(s.embedding_sinusoid_base), dtype=torch.float64),
+                             -2.0 * i / s.hidden_size)
+            self._sinusoid_inv_freq = freq.to(torch.float32).to(self.env.device)
+        return self._sinusoid_inv_freq
+
     # ---- one step -------------------------------------------------------
     def forward(self, step) -> torch.Tensor:
         T = step.num_tokens
@@ -150,8 +169,15 @@ class DecoderModel:
             ops.clear_page_tails(pages, page_dim, step.positions, step.token_seq, step.block_tables[g],
                                  step.context_lens)
         x = ws.get("model.residual", (T, s.hidden_size), torch.float32)
-        ops.embed_gather(step.token_ids, self.embedding, x,
-                         s.embedding_scale if s.embedding_scale is not None else 1.0)
+        scale = s.embedding_scale if s.embedding_scale is not None else 1.0
+        if s.embedding_sinusoid_base is not None or self.embedding_norm is not None:
+            # position vector and norm of the embedding row in the kernel that gathers it
+            norm = self.embedding_norm
+            ops.embed_sinusoid_norm(step.token_ids, step.positions, self.embedding, self._sinusoid_frequencies(),
+                                    norm.weight if norm is not None else None, norm.eps if norm is not None else 0.0,
+                                    x, scale)
+        else:
+            ops.embed_gather(step.token_ids, self.embedding, x, scale)
         delta = None
         for r, run in enumerate(s.order):
             delta = self.blocks[run.layer].forward(x, delta, step, self.caches[r])

@@ -39,13 +39,15 @@ def known_architectures():
 def resolve(config: Mapping[str, Any]) -> Architecture:
     """The architecture a raw config.json dictionary names."""
     names = list(config.get("architectures") or [])
+    if isinstance(config.get("architecture"), str):
+        names.append(config["architecture"])          # configurations that name one architecture, in the singular
     if config.get("model_type"):
         names.append(config["model_type"])
     for n in names:
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]
     raise ConfigError(
-        f"no model is registered for architectures {config.get('architectures')!r} / "
+        f"no model is registered for architectures {config.get('architectures') or config.get('architecture')!r} / "
         f"model_type {config.get('model_type')!r} (known: {', '.join(known_architectures())})")
 
 

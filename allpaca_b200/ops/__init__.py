@@ -726,3 +726,10 @@ def check_kernel_status() -> None:
     if code != 0:
         raise KernelError(f"the tensor-core matrix product gave up waiting (code {code}: "
                           f"1 free stage, 2 operands, 3 accumulator); its results are void")
+
+
+from .mixers import (attention_window_bias, causal_conv_silu, embed_sinusoid_norm, gated_group_rmsnorm,  # noqa: E402
+                     qk_norm_store, ssm_scan)
+from . import routed  # noqa: E402,F401
+from .routed import (gated_act, moe_combine, moe_down, moe_gate_up, moe_max_tiles, moe_route,  # noqa: E402
+                     moe_sort)

@@ -36,6 +36,34 @@ _CORE_SIGNATURES = {
     "ap_sample": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
     "ap_sample_rows": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
     "ap_sample_cluster": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P],
+    # int ap_embed_sinusoid_norm(tokens, positions, table, table_dtype, inv_freq, norm_w, norm_dtype, eps, scale,
+    #                            x, T, H, V, stream)
+    "ap_embed_sinusoid_norm": [_P, _P, _P, _I, _P, _P, _I, _F, _F, _P, _I, _I, _I, _P],
+    # int ap_qk_norm_store(in, in_dtype, ld_in, q_out, cache, act_dtype, positions, token_seq, block_table,
+    #                      max_blocks, T, nh, nkv, D, VD, P, page_stride, eps, normalise, temp_coef, temp_every, stream)
+    "ap_qk_norm_store": [_P, _I, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _F, _I, _P],
+    # int ap_attention_window_bias(q, out, cache, dtype, block_table, max_blocks, seq_start, positions, nseq, T,
+    #                              nh, nkv, D, VD, P, page_stride, scale, window, r1, r2, stream)
+    "ap_attention_window_bias": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P, _P],
+    # int ap_causal_conv_silu(in, ld_in, col0, w, bias, state, state_stride, token_seq, seq_start, positions,
+    #                         state_slots, out, T, nseq, C, taps, stream)
+    "ap_causal_conv_silu": [_P, _L, _I, _P, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    # int ap_ssm_scan(xbc, ld_xbc, dt_raw, ld_dt, dt_bias, a_log, d_skip, state, state_stride, seq_start, positions,
+    #                 state_slots, y, T, nseq, heads, groups, N, vdim, stream)
+    "ap_ssm_scan": [_P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    # int ap_gated_group_rmsnorm(y, z, ld_z, w, w_dtype, eps, out, out_dtype, T, inner, parts, stream)
+    "ap_gated_group_rmsnorm": [_P, _P, _L, _P, _I, _F, _P, _I, _I, _I, _I, _P],
+    # int ap_gated_act(in, in_dtype, out, out_dtype, T, I, pairs, act, limit, alpha, shift, stream)
+    "ap_gated_act": [_P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P],
+    "ap_moe_route": [_P, _P, _P, _P, _I, _I, _I, _P],
+    "ap_moe_max_tiles": [_I, _I],
+    "ap_moe_sort": [_P, _P, _P, _P, _I, _I, _P],
+    # int ap_moe_gate_up(a, a_dtype, w, w_dtype, y, y_dtype, perm, top, tiles, pairs, E, F, K, act, limit, alpha,
+    #                    shift, stream)
+    "ap_moe_gate_up": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P],
+    # int ap_moe_down(y, y_dtype, w, w_dtype, o, tiles, pairs, E, H, F, stream)
+    "ap_moe_down": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P],
+    "ap_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _P],
 }
 _OPTIONAL_CORE_SIGNATURES = {
     # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, reduce, epi,

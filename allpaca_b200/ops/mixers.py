@@ -1,0 +1,194 @@
+"""Python faces of the kernels of the mixers beyond rotary attention, and of the embedding
+with a position vector: argument checks, then one C call each (see ``ops/__init__.py``)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import AP_F32, KernelError, _check, call, core, dtype_code, stream_handle
+
+
+def embed_sinusoid_norm(tokens: torch.Tensor, positions: torch.Tensor, table: torch.Tensor,
+                        inv_freq: Optional[torch.Tensor], norm_weight: Optional[torch.Tensor], eps: float,
+                        x: torch.Tensor, scale: float = 1.0) -> None:
+    """``x[t] = norm(table[tokens[t]] * scale + sinusoid(positions[t]))`` into the 32-bit residual.
+
+    The position vector has ``sin(p * inv_freq[i])`` at entry ``2i`` and the cosine at ``2i + 1``
+    (``inv_freq`` None: no position vector); the norm is an RMS norm with the weight vector
+    ``norm_weight [H]`` (None: no norm)."""
+    _check(tokens, "tokens", torch.int32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    _check(table, "table", dims=2)
+    _check(x, "x", torch.float32, 2)
+    T, H = x.shape
+    if tokens.shape[0] != T or positions.shape[0] < T or table.shape[1] != H:
+        raise KernelError("embed_sinusoid_norm: shapes disagree")
+    if inv_freq is not None:
+        _check(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] * 2 != H:
+            raise KernelError("embed_sinusoid_norm: one frequency per pair of entries is needed")
+    if norm_weight is not None:
+        _check(norm_weight, "norm_weight", dims=1)
+        if norm_weight.shape[0] != H:
+            raise KernelError("embed_sinusoid_norm: the norm's weight must have one entry per column")
+    call(core(), "ap_embed_sinusoid_norm", tokens.data_ptr(), positions.data_ptr(), table.data_ptr(),
+         dtype_code(table.dtype), inv_freq.data_ptr() if inv_freq is not None else 0,
+         norm_weight.data_ptr() if norm_weight is not None else 0,
+         dtype_code(norm_weight.dtype) if norm_weight is not None else AP_F32, float(eps), float(scale),
+         x.data_ptr(), T, H, table.shape[0], stream_handle())
+
+
+def _kv_pages(cache_layer: torch.Tensor, num_kv_heads: int, key_dim: int, value_dim: int, name: str):
+    """(P, page stride) of pages ``[pages, nkv, P, key_dim + value_dim]``."""
+    if cache_layer.dim() != 4 or cache_layer.shape[1] != num_kv_heads or cache_layer.shape[3] != key_dim + value_dim:
+        raise KernelError(f"{name}: pages {tuple(cache_layer.shape)} are not [pages, {num_kv_heads}, P, "
+                          f"{key_dim} + {value_dim}]")
+    if cache_layer.stride(3) != 1 or cache_layer.stride(2) != key_dim + value_dim \
+            or cache_layer.stride(1) != cache_layer.shape[2] * (key_dim + value_dim):
+        raise KernelError(f"{name}: a page must be contiguous")
+    return cache_layer.shape[2], cache_layer.stride(0)
+
+
+def qk_norm_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[torch.Tensor],
+                  positions: torch.Tensor, token_seq: torch.Tensor, block_table: Optional[torch.Tensor],
+                  num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, eps: float,
+                  normalise: bool = True, temp_coef: float = 0.0, temp_every: int = 0) -> None:
+    """Prepare the operands of :func:`attention_window_bias` from the stacked projection
+    ``qkv [T, nh*D + nkv*D + nkv*VD]``: every query and key head divided by its root mean square
+    (``normalise``), queries multiplied by ``1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)``
+    (``temp_every`` 0: no temperature) into ``q_out [T, nh*D]``, keys and values into the pages
+    ``cache_layer [pages, nkv, P, D + VD]`` (None: not stored)."""
+    _check(qkv, "qkv", dims=2)
+    _check(q_out, "q_out", dims=2)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim \
+            or q_out.shape[0] < T or q_out.shape[1] != num_heads * key_dim:
+        raise KernelError(f"qk_norm_store: shapes disagree: qkv {tuple(qkv.shape)}, q_out {tuple(q_out.shape)}")
+    _check(positions, "positions", torch.int32, 1)
+    P, page_stride, cptr, tsptr, btptr, maxb = 1, 0, 0, 0, 0, 0
+    if cache_layer is not None:
+        if cache_layer.dtype != q_out.dtype:
+            raise KernelError("qk_norm_store: the pages must have the queries' type")
+        P, page_stride = _kv_pages(cache_layer, num_kv_heads, key_dim, value_dim, "qk_norm_store")
+        _check(token_seq, "token_seq", torch.int32, 1)
+        _check(block_table, "block_table", torch.int32, 2)
+        cptr, tsptr, btptr, maxb = cache_layer.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), \
+            block_table.shape[1]
+    call(core(), "ap_qk_norm_store", qkv.data_ptr(), dtype_code(qkv.dtype), qkv.stride(0), q_out.data_ptr(), cptr,
+         dtype_code(q_out.dtype), positions.data_ptr(), tsptr, btptr, maxb, T, num_heads, num_kv_heads, key_dim,
+         value_dim, P, page_stride, float(eps), 1 if normalise else 0, float(temp_coef), int(temp_every),
+         stream_handle())
+
+
+def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor,
+                          seq_start: torch.Tensor, positions: torch.Tensor, num_seqs: int, num_heads: int,
+                          num_kv_heads: int, key_dim: int, value_dim: int, scale: float, window: int = 0,
+                          r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of ``q [T, nh*D]`` over pages ``[pages, nkv, P, D + VD]`` into
+    ``out [T, nh*VD]``: ``score = q.k * scale - r1[h] * ln(1 + r2[h] * distance)`` (``r1``, ``r2``
+    32-bit ``[nh]`` or None), over the last ``window`` keys (0: all), ordinary softmax, 32-bit."""
+    _check(q, "q", dims=2)
+    _check(out, "out", q.dtype, 2)
+    T = q.shape[0]
+    if q.shape[1] != num_heads * key_dim or tuple(out.shape) != (T, num_heads * value_dim):
+        raise KernelError("attention_window_bias: q/out do not match the heads")
+    if cache_layer.dtype != q.dtype:
+        raise KernelError("attention_window_bias: the pages must have the queries' type")
+    P, page_stride = _kv_pages(cache_layer, num_kv_heads, key_dim, value_dim, "attention_window_bias")
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(seq_start, "seq_start", torch.int32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    if seq_start.shape[0] < num_seqs + 1 or block_table.shape[0] < num_seqs:
+        raise KernelError("attention_window_bias: seq_start or the block table is shorter than the sequences")
+    for t, n in ((r1, "r1"), (r2, "r2")):
+        if t is not None:
+            _check(t, n, torch.float32, 1)
+            if t.shape[0] != num_heads:
+                raise KernelError(f"attention_window_bias: {n} must have one entry per head")
+    call(core(), "ap_attention_window_bias", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(), dtype_code(q.dtype),
+         block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(), positions.data_ptr(), int(num_seqs), T,
+         num_heads, num_kv_heads, key_dim, value_dim, P, page_stride, float(scale), int(window or 0),
+         r1.data_ptr() if r1 is not None else 0, r2.data_ptr() if r2 is not None else 0, stream_handle())
+
+
+def causal_conv_silu(inp: torch.Tensor, col0: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                     state: Optional[torch.Tensor], token_seq: torch.Tensor, seq_start: torch.Tensor,
+                     positions: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor, num_seqs: int) -> None:
+    """``out[t, c] = silu(bias[c] + sum_j weight[c, j] * in[t - (taps-1) + j, col0 + c])`` per
+    sequence, zeros before position 0; ``state [slots, taps-1, C]`` (32-bit, may be a strided
+    view of the slots' rows) supplies the inputs from before the step and is brought up to date."""
+    _check(inp, "in", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 2)
+    _check(out, "out", torch.float32, 2)
+    T, C = out.shape
+    taps = weight.shape[1]
+    if weight.shape[0] != C or inp.shape[0] < T or inp.shape[1] < col0 + C:
+        raise KernelError("causal_conv_silu: shapes disagree")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+    sptr, sstride = 0, 0
+    if taps > 1:
+        if state is None or state.dtype != torch.float32 or state.dim() != 3 \
+                or tuple(state.shape[1:]) != (taps - 1, C) or state.stride(2) != 1 or state.stride(1) != C:
+            raise KernelError("causal_conv_silu: the state must be 32-bit [slots, taps-1, C] with contiguous rows")
+        sptr, sstride = state.data_ptr(), state.stride(0)
+    for t, n in ((token_seq, "token_seq"), (seq_start, "seq_start"), (positions, "positions"),
+                 (state_slots, "state_slots")):
+        _check(t, n, torch.int32, 1)
+    call(core(), "ap_causal_conv_silu", inp.data_ptr(), inp.stride(0), int(col0), weight.data_ptr(),
+         bias.data_ptr() if bias is not None else 0, sptr, sstride, token_seq.data_ptr(), seq_start.data_ptr(),
+         positions.data_ptr(), state_slots.data_ptr(), out.data_ptr(), T, int(num_seqs), C, taps, stream_handle())
+
+
+def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: Optional[torch.Tensor], a_log: torch.Tensor,
+             d_skip: Optional[torch.Tensor], state: torch.Tensor, seq_start: torch.Tensor, positions: torch.Tensor,
+             state_slots: torch.Tensor, y: torch.Tensor, num_seqs: int, heads: int, groups: int, state_size: int,
+             value_dim: int) -> None:
+    """The recurrence of a selective state-space layer with one decay per head, all 32-bit:
+    ``dt = softplus(dt_raw + dt_bias)``, ``S = exp(-exp(a_log) dt) S + dt B x^T``,
+    ``y = S^T C + d_skip x``.  ``xbc [T, heads*vdim + 2*groups*N]`` holds x, B and C side by side;
+    ``dt_raw [T, heads]`` may be a strided view; ``state [slots, heads, N, vdim]`` may be a strided
+    view of the slots' rows.  A sequence whose first row has position 0 starts from zero."""
+    _check(xbc, "xbc", torch.float32, 2)
+    _check(y, "y", torch.float32, 2)
+    T = y.shape[0]
+    inner = heads * value_dim
+    if tuple(xbc.shape) != (T, inner + 2 * groups * state_size) or y.shape[1] != inner:
+        raise KernelError("ssm_scan: xbc/y do not match the sizes")
+    if dt_raw.dtype != torch.float32 or dt_raw.dim() != 2 or dt_raw.shape[0] < T or dt_raw.shape[1] != heads \
+            or dt_raw.stride(1) != 1:
+        raise KernelError("ssm_scan: dt_raw must be 32-bit [T, heads] with contiguous rows")
+    if state.dtype != torch.float32 or state.dim() != 4 or tuple(state.shape[1:]) != (heads, state_size, value_dim) \
+            or not state[0].is_contiguous():
+        raise KernelError("ssm_scan: the state must be 32-bit [slots, heads, N, vdim] with contiguous rows")
+    for t, n in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip")):
+        if t is not None:
+            _check(t, n, torch.float32, 1)
+            if t.shape[0] != heads:
+                raise KernelError(f"ssm_scan: {n} must have one entry per head")
+    for t, n in ((seq_start, "seq_start"), (positions, "positions"), (state_slots, "state_slots")):
+        _check(t, n, torch.int32, 1)
+    call(core(), "ap_ssm_scan", xbc.data_ptr(), xbc.stride(0), dt_raw.data_ptr(), dt_raw.stride(0),
+         dt_bias.data_ptr() if dt_bias is not None else 0, a_log.data_ptr(),
+         d_skip.data_ptr() if d_skip is not None else 0, state.data_ptr(), state.stride(0), seq_start.data_ptr(),
+         positions.data_ptr(), state_slots.data_ptr(), y.data_ptr(), T, int(num_seqs), heads, groups, state_size,
+         value_dim, stream_handle())
+
+
+def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: Optional[torch.Tensor], eps: float,
+                        out: torch.Tensor, parts: int) -> None:
+    """``out = rmsnorm(y * silu(z)) * weight`` with the root mean square taken over each of
+    ``parts`` equal parts of a row; ``y [T, inner]`` 32-bit, ``z`` a 32-bit (strided) view of the
+    same shape."""
+    _check(y, "y", torch.float32, 2)
+    _check(out, "out", dims=2)
+    T, inner = y.shape
+    if z.dtype != torch.float32 or z.dim() != 2 or z.shape[0] < T or z.shape[1] != inner or z.stride(1) != 1 \
+            or tuple(out.shape) != (T, inner):
+        raise KernelError("gated_group_rmsnorm: shapes disagree")
+    if weight is not None:
+        _check(weight, "weight", dims=1)
+    call(core(), "ap_gated_group_rmsnorm", y.data_ptr(), z.data_ptr(), z.stride(0),
+         weight.data_ptr() if weight is not None else 0, dtype_code(weight.dtype) if weight is not None else AP_F32,
+         float(eps), out.data_ptr(), dtype_code(out.dtype), T, inner, int(parts), stream_handle())

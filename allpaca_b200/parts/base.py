@@ -320,6 +320,11 @@ class ModelSpec:
     max_position_embeddings: int = 2048
     # Ends of the stack that some decoders alter; all default to "as it is".
     embedding_scale: Optional[float] = None      # the gathered embedding row is multiplied by it
+    # a sinusoidal position vector added to the embedding row: entry 2i is sin(p * base^(-2i/width)),
+    # entry 2i+1 the cosine of the same angle (None: no position vector)
+    embedding_sinusoid_base: Optional[float] = None
+    embedding_norm: Optional[PartSpec] = None    # a norm applied to the embedding row (after the position vector)
+    embedding_norm_prefix: str = "model.embed_norm."
     head_bias_name: Optional[str] = None         # a [vocab] tensor added to the logits
     logit_scale: Optional[float] = None          # logits are multiplied by it ...
     logit_softcap: Optional[float] = None        # ... and then become cap * tanh(logit / cap)

@@ -19,23 +19,28 @@ from .norm import RMSNorm
 @register("block", "prenorm")
 class PreNormBlock(Block):
     """Parameters: ``hidden_size`` and four :class:`PartSpec`: ``mixer``, ``feed_forward``,
-    ``mixer_norm``, ``feed_forward_norm``; and the weight-name prefixes ``mixer_prefix``,
+    ``mixer_norm``, ``feed_forward_norm`` (``feed_forward`` None: the layer is its mixer alone);
+    and the weight-name prefixes ``mixer_prefix``,
     ``feed_forward_prefix``, ``mixer_norm_prefix``, ``feed_forward_norm_prefix``."""
 
     def __init__(self, params, env: BuildEnv):
         super().__init__(params, env)
-        self.require("hidden_size", "mixer", "feed_forward", "mixer_norm", "feed_forward_norm")
+        self.require("hidden_size", "mixer", "mixer_norm")
         self.hidden = int(params["hidden_size"])
         self.mixer = build("mixer", params["mixer"], env)
-        self.feed_forward = build("feed_forward", params["feed_forward"], env)
         self.mixer_norm = build("norm", params["mixer_norm"], env)
-        self.feed_forward_norm = build("norm", params["feed_forward_norm"], env)
         self._prefixes = {
             params.get("mixer_prefix", "mixer."): self.mixer,
-            params.get("feed_forward_prefix", "feed_forward."): self.feed_forward,
             params.get("mixer_norm_prefix", "mixer_norm."): self.mixer_norm,
-            params.get("feed_forward_norm_prefix", "feed_forward_norm."): self.feed_forward_norm,
         }
+        # a layer may have no feed-forward (``feed_forward`` None): then it has no second norm either
+        self.feed_forward = self.feed_forward_norm = None
+        if params.get("feed_forward") is not None:
+            self.require("feed_forward_norm")
+            self.feed_forward = build("feed_forward", params["feed_forward"], env)
+            self.feed_forward_norm = build("norm", params["feed_forward_norm"], env)
+            self._prefixes[params.get("feed_forward_prefix", "feed_forward.")] = self.feed_forward
+            self._prefixes[params.get("feed_forward_norm_prefix", "feed_forward_norm.")] = self.feed_forward_norm
 
         self.fused = False
 
@@ -48,7 +53,7 @@ class PreNormBlock(Block):
         runs without norm kernels (the products scale their result rows by the root mean square,
         which the product before them summed up while it added into the residual); a step of many
         rows runs the norm kernels as before, without their weights."""
-        if self.env.dtype != torch.bfloat16:
+        if self.env.dtype != torch.bfloat16 or self.feed_forward is None:
             return
         if not (type(self.mixer_norm) is RMSNorm and type(self.feed_forward_norm) is RMSNorm):
             return
@@ -80,5 +85,7 @@ class PreNormBlock(Block):
             delta = None                 # the block before has added into the residual itself
         self.mixer_norm.forward(x, h, delta=delta)
         delta = self.mixer.forward(h, step, cache)
+        if self.feed_forward is None:
+            return delta
         self.feed_forward_norm.forward(x, h, delta=delta)
         return self.feed_forward.forward(h, step)

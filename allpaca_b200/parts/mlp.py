@@ -21,7 +21,9 @@ from .linear import Linear
 @register("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
     """Parameters: ``hidden_size``, ``intermediate_size``, ``bias`` (False: no biases, as on the
-    Llama path)."""
+    Llama path), ``activation`` of the gate (``"silu"``, or ``"relu"``: then the activation is a
+    kernel of its own after the product, and the norm before is not folded in), ``names`` (the
+    local tensor names of gate, up and down; default ``gate_proj.weight`` and so on)."""
 
     def __init__(self, params, env: BuildEnv):
         super().__init__(params, env)
@@ -29,13 +31,19 @@ class SwiGLU(FeedForward):
         self.hidden = int(params["hidden_size"])
         self.inter = int(params["intermediate_size"])
         self.bias = bool(params.get("bias", False))
+        self.activation = str(params.get("activation", "silu"))
+        ops.routed.activation_code(self.activation)          # refuses an unknown name
+        names = params.get("names") or ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+        self.gate_name, self.up_name, self.down_name = names
+        if self.bias and params.get("names"):
+            raise ValueError("a gated feed-forward with biases keeps the default tensor names")
         self.gate_up = Linear(env, 2 * self.inter, self.hidden)
         self.down = Linear(env, self.hidden, self.inter)
 
     def weights(self) -> Dict[str, WeightSpec]:
-        w = {"gate_proj.weight": WeightSpec((self.inter, self.hidden)),
-             "up_proj.weight": WeightSpec((self.inter, self.hidden)),
-             "down_proj.weight": WeightSpec((self.hidden, self.inter))}
+        w = {self.gate_name: WeightSpec((self.inter, self.hidden)),
+             self.up_name: WeightSpec((self.inter, self.hidden)),
+             self.down_name: WeightSpec((self.hidden, self.inter))}
         if self.bias:
             w.update({"gate_proj.bias": WeightSpec((self.inter,), "bias"),
                       "up_proj.bias": WeightSpec((self.inter,), "bias"),
@@ -43,14 +51,14 @@ class SwiGLU(FeedForward):
         return w
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        gate, up = tensors[self.gate_name], tensors[self.up_name]
         gu_bias = torch.stack([tensors["gate_proj.bias"], tensors["up_proj.bias"]], dim=1).reshape(-1) \
             if self.bias else None
         self.gate_up.load(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden), gu_bias)
-        self.down.load(tensors["down_proj.weight"], tensors["down_proj.bias"] if self.bias else None)
+        self.down.load(tensors[self.down_name], tensors["down_proj.bias"] if self.bias else None)
 
     def can_fold_input_norm(self) -> bool:
-        return self.gate_up.fusable() and self.down.fusable()
+        return self.activation == "silu" and self.gate_up.fusable() and self.down.fusable()
 
     def fold_input_norm(self, weight: torch.Tensor) -> None:
         """Multiply the weight of the norm before this feed-forward into its first product."""
@@ -67,6 +75,11 @@ class SwiGLU(FeedForward):
 
     def forward(self, h: torch.Tensor, step) -> torch.Tensor:
         T = h.shape[0]
+        if self.activation != "silu":
+            gu = self.gate_up.forward(h, "ffn.gate_up", "either")
+            act = self.env.workspace.get("ffn.act", (T, self.inter), self.env.dtype)
+            ops.gated_act(gu, act, self.activation, pairs=True)
+            return self.down.forward(act, "ffn.down", "delta")
         act = self.gate_up.forward_gated(h, "ffn.act")        # one kernel when there are many rows
         if act is None:
             gu = self.gate_up.forward(h, "ffn.gate_up", "either")

@@ -1,0 +1,87 @@
+"""A routed feed-forward: ``experts`` small gated feed-forward layers, of which every row uses
+the ``top`` whose router logits are largest.
+
+Router logits ``z = W_router h + b`` are 32-bit; the chosen experts' weights are the softmax
+over the chosen logits only; the output is the weighted sum of the chosen experts' outputs.
+An expert is ``W_down act(W_gate h, W_up h)`` without biases, ``act`` one of the gated
+activations of ``ops.gated_act`` (``clamped_sigmoid``: ``g' = min(g, limit)``,
+``u' = clamp(u, -limit, limit)``, ``g' sigmoid(alpha g') (u' + shift)``).
+
+On the device the (row, choice) pairs are grouped by expert, every expert's rows run through
+its two products in tiles, and a last pass adds each row's weighted results in the order of
+its choices.  Counts and tiles never leave the device, so a step can be replayed from a CUDA
+graph, and a row's result does not depend on what else is in the batch.
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping
+
+import torch
+
+from .. import ops
+from .base import BuildEnv, FeedForward, PartError, WeightSpec, register
+
+
+@register("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    """Parameters: ``hidden_size``, ``expert_size``, ``experts``, ``top``, ``activation``
+    (``"clamped_sigmoid"``), ``limit``, ``alpha`` (1.702), ``shift`` (1.0), ``router_bias`` (True);
+    tensors ``router`` ``[experts, hidden]``, ``router.b`` ``[experts]`` and, per expert ``i``,
+    ``e<i>.gate``, ``e<i>.up`` ``[expert_size, hidden]`` and ``e<i>.down`` ``[hidden, expert_size]``."""
+
+    def __init__(self, params, env: BuildEnv):
+        super().__init__(params, env)
+        self.require("hidden_size", "expert_size", "experts", "top")
+        p = params
+        self.hidden, self.inter = int(p["hidden_size"]), int(p["expert_size"])
+        self.experts, self.top = int(p["experts"]), int(p["top"])
+        if not (0 < self.top <= self.experts) or self.experts > 256 or self.top > 16:
+            raise PartError(f"{self.top} of {self.experts} experts is not a routing the kernels take "
+                            f"(at most 16 of at most 256)")
+        self.activation = str(p.get("activation", "clamped_sigmoid"))
+        ops.routed.activation_code(self.activation)
+        self.limit = float(p.get("limit", 0.0))
+        self.alpha = float(p.get("alpha", 1.702))
+        self.shift = float(p.get("shift", 1.0))
+        self.router_bias = bool(p.get("router_bias", True))
+        if self.activation == "clamped_sigmoid" and not self.limit > 0:
+            raise PartError("the clamped activation needs a positive limit")
+
+    def weights(self) -> Dict[str, WeightSpec]:
+        w = {"router": WeightSpec((self.experts, self.hidden))}
+        if self.router_bias:
+            w["router.b"] = WeightSpec((self.experts,), "bias")
+        for e in range(self.experts):
+            w[f"e{e}.gate"] = WeightSpec((self.inter, self.hidden))
+            w[f"e{e}.up"] = WeightSpec((self.inter, self.hidden))
+            w[f"e{e}.down"] = WeightSpec((self.hidden, self.inter))
+        return w
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.router = tensors["router"].contiguous()
+        self.router_b = tensors["router.b"].float().contiguous() if self.router_bias else None
+        # [experts, 2 F, hidden]: an expert's gate rows, then its up rows; [experts, hidden, F]
+        self.gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
+                                    for e in range(self.experts)]).contiguous()
+        self.down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
+
+    def forward(self, h: torch.Tensor, step) -> torch.Tensor:
+        T = h.shape[0]
+        ws = self.env.workspace
+        pairs = T * self.top
+        logits = ws.get("moe.logits", (T, self.experts), torch.float32)
+        ops.gemm_simt(h, self.router, logits)                       # 32-bit sums on the CUDA cores
+        chosen = ws.get("moe.chosen", (T, self.top), torch.int32)
+        weight = ws.get("moe.weight", (T, self.top), torch.float32)
+        ops.moe_route(logits, self.router_b, chosen, weight)
+        perm = ws.get("moe.perm", (pairs,), torch.int32)
+        place = ws.get("moe.place", (pairs,), torch.int32)
+        tiles = ws.get("moe.tiles", (ops.moe_max_tiles(pairs, self.experts) + 1, 3), torch.int32)
+        ops.moe_sort(chosen, perm, place, tiles, self.experts)
+        y = ws.get("moe.act", (pairs, self.inter), self.env.dtype)
+        ops.moe_gate_up(h, self.gate_up, y, perm, self.top, tiles, self.activation, self.limit, self.alpha, self.shift)
+        o = ws.get("moe.out", (pairs, self.hidden), torch.float32)
+        ops.moe_down(y, self.down, o, tiles)
+        delta = ws.get("moe.delta", (1, T, self.hidden), torch.float32)
+        ops.moe_combine(o, place, weight, delta[0])
+        return delta

@@ -16,21 +16,28 @@ from .base import BuildEnv, Norm, WeightSpec, register
 
 @register("norm", "rmsnorm")
 class RMSNorm(Norm):
-    """Parameters: ``size`` (width of a row), ``eps``."""
+    """Parameters: ``size`` (width of a row), ``eps``, ``scalar_weight`` (False; True: the
+    checkpoint holds one number for all coordinates, a tensor without dimensions), ``weight_name``
+    (``"weight"``: the tensor's name behind the part's prefix; may be empty, the prefix then is
+    the whole name)."""
 
     def __init__(self, params, env: BuildEnv):
         super().__init__(params, env)
         self.require("size", "eps")
         self.size = int(params["size"])
         self.eps = float(params["eps"])
+        self.scalar_weight = bool(params.get("scalar_weight", False))
+        self.weight_name = str(params.get("weight_name", "weight"))
         self.weight = None
         self._kernel_weight = None
 
     def weights(self) -> Dict[str, WeightSpec]:
-        return {"weight": WeightSpec((self.size,), "norm")}
+        return {self.weight_name: WeightSpec(() if self.scalar_weight else (self.size,), "norm")}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        w = tensors[self.weight_name]
+        # one number for all coordinates: the kernels take it as a vector of equal entries
+        self.weight = (w.reshape(1).expand(self.size) if self.scalar_weight else w).contiguous()
         self._kernel_weight = self.weight
 
     def fold(self) -> None:
