@@ -119,7 +119,7 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
                              const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_start,
                              const int* __restrict__ positions, int nseq, int nh, int nkv, int D, int VD, int P,
                              size_t page_stride, float scale, int window, const float* __restrict__ r1,
-                             const float* __restrict__ r2) {
+                             const float* __restrict__ r2, int skip_single) {
     extern __shared__ __align__(16) float smem[];
     ap_pdl_trigger();
     ap_pdl_wait();
@@ -127,7 +127,7 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
     int b = blockIdx.x, seq = -1, row0 = 0, nrows = 0;
     for (int s = 0; s < nseq; ++s) {
         const int a = seq_start[s], n = seq_start[s + 1] - a;
-        const int tiles = (n + QT - 1) / QT;
+        const int tiles = (skip_single && n == 1) ? 0 : (n + QT - 1) / QT;
         if (b < tiles) {
             seq = s;
             row0 = a + b * QT;
@@ -164,11 +164,14 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
     }
     const int nc = (VD + 31) / 32;
     const int my_rows = min(RPW, nrows - warp * RPW);        // <= 0: this warp only helps loading
-    for (int k0 = klo; k0 <= pos_last; k0 += KT) {
+    // Key tiles start at multiples of KT whatever the rows of this CTA are: a row then meets its
+    // keys in the same tiles and lanes however its prompt was cut, and gets the same bits.  Keys
+    // before klo are not loaded (their pages may have gone back to the pool); no row sees them.
+    for (int k0 = klo / KT * KT; k0 <= pos_last; k0 += KT) {
         __syncthreads();                                     // the tile before is consumed (and q_s is written)
         for (int j = warp; j < KT; j += AWB_WARPS) {
             const int kp = k0 + j;
-            if (kp <= pos_last) {
+            if (kp >= klo && kp <= pos_last) {
                 const int page = table[kp / P];
                 const TA* src = cache + (size_t)page * page_stride + ((size_t)kvh * P + kp % P) * (D + VD);
                 for (int d = lane; d < D; d += 32) k_s[j * DP + d] = ap_to_float(src[d]);
@@ -240,10 +243,157 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Sequences that bring one row (decoding).  One CTA per (sequence, key/value head): the query
+// heads that share the key/value head are served together, so every key and value is read
+// once for all of them.  The four warps take the key tiles in turn (tile i goes to warp
+// i mod 4), each with an online softmax of its own; a lane reads its key's row straight from
+// the page, values come row by row with the lanes across the columns; at the end the warps'
+// partial results meet in shared memory and are merged in warp order.  Sequences with
+// another number of rows are left to the kernel above (`skip_single` there).
+// ---------------------------------------------------------------------------------------
+#define DEC_REP 8                 // query heads per CTA at most (more: the grid's z walks them)
+
+template <typename TA>
+__global__ void __launch_bounds__(AWB_THREADS)
+attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ out, const TA* __restrict__ cache,
+                                    const int* __restrict__ block_table, int max_blocks,
+                                    const int* __restrict__ seq_start, const int* __restrict__ positions, int nh,
+                                    int nkv, int D, int VD, int P, size_t page_stride, float scale, int window,
+                                    const float* __restrict__ r1, const float* __restrict__ r2) {
+    extern __shared__ __align__(16) float smem[];
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    const int seq = blockIdx.x, kvh = blockIdx.y;
+    const int row = seq_start[seq];
+    if (seq_start[seq + 1] - row != 1) return;
+    const int rep_all = nh / nkv;
+    const int h0 = kvh * rep_all + blockIdx.z * DEC_REP;
+    const int rep = min(DEC_REP, rep_all - (int)blockIdx.z * DEC_REP);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int NC = MAX_HEAD / 32;
+    float* q_s = smem;                                   // [DEC_REP][D]
+    float* p_s = q_s + DEC_REP * D;                      // [AWB_WARPS][DEC_REP][KT]
+    float* part = p_s + AWB_WARPS * DEC_REP * KT;        // [AWB_WARPS][DEC_REP][VD + 2]
+    for (int i = threadIdx.x; i < rep * D; i += AWB_THREADS)
+        q_s[i] = ap_to_float(q[((size_t)row * nh + h0) * D + i]);
+    __syncthreads();
+    const int qpos = positions[row];
+    const int* table = block_table + (size_t)seq * max_blocks;
+    const int klo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
+    float acc[DEC_REP][NC], m[DEC_REP], l[DEC_REP], b1[DEC_REP], b2[DEC_REP];
+#pragma unroll
+    for (int i = 0; i < DEC_REP; ++i) {
+        m[i] = -FLT_MAX;
+        l[i] = 0.f;
+        b1[i] = (r1 && i < rep) ? r1[h0 + i] : 0.f;
+        b2[i] = (r2 && i < rep) ? r2[h0 + i] : 0.f;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[i][c] = 0.f;
+    }
+    const int nc = (VD + 31) / 32;
+    float* pw = p_s + warp * DEC_REP * KT;
+    const int first_tile = klo / KT;
+    for (int tile = first_tile + warp; tile * KT <= qpos; tile += AWB_WARPS) {
+        const int kp = tile * KT + lane;
+        const bool seen = kp >= klo && kp <= qpos;
+        float s[DEC_REP];
+#pragma unroll
+        for (int i = 0; i < DEC_REP; ++i) s[i] = 0.f;
+        if (seen) {
+            const TA* kr = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * (D + VD);
+            if (sizeof(TA) == 2 && D % 8 == 0 && (D + VD) % 8 == 0 && (page_stride % 8) == 0 &&
+                ((uintptr_t)cache & 15) == 0) {
+                // eight 16-bit elements of the key's row per load
+                for (int d = 0; d < D; d += 8) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(kr) + d);
+                    const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 kv = __bfloat1622float2(k2[e]);
+#pragma unroll
+                        for (int i = 0; i < DEC_REP; ++i)
+                            if (i < rep) s[i] = fmaf(q_s[i * D + d + 2 * e + 1], kv.y, fmaf(q_s[i * D + d + 2 * e], kv.x, s[i]));
+                    }
+                }
+            } else {
+                for (int d = 0; d < D; ++d) {
+                    const float kv = ap_to_float(kr[d]);
+#pragma unroll
+                    for (int i = 0; i < DEC_REP; ++i)
+                        if (i < rep) s[i] = fmaf(q_s[i * D + d], kv, s[i]);
+                }
+            }
+        }
+        const float dist = (float)(qpos - kp);
+#pragma unroll
+        for (int i = 0; i < DEC_REP; ++i) {
+            const float sc = seen ? s[i] * scale - b1[i] * log1pf(b2[i] * dist) : -FLT_MAX;
+            const float m_new = fmaxf(m[i], ap_warp_max(sc));
+            const float p = seen ? expf(sc - m_new) : 0.f;
+            const float alpha = expf(m[i] - m_new);
+            l[i] = l[i] * alpha + ap_warp_sum(p);
+            m[i] = m_new;
+            pw[i * KT + lane] = p;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) acc[i][c] *= alpha;
+        }
+        __syncwarp();
+        const int last = min(KT, qpos - tile * KT + 1);
+        for (int j = max(0, klo - tile * KT); j < last; ++j) {
+            const int kj = tile * KT + j;
+            const TA* vr = cache + (size_t)table[kj / P] * page_stride + ((size_t)kvh * P + kj % P) * (D + VD) + D;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                if (c < nc) {
+                    const int d = lane + 32 * c;
+                    const float vv = d < VD ? ap_to_float(vr[d]) : 0.f;
+#pragma unroll
+                    for (int i = 0; i < DEC_REP; ++i)
+                        if (i < rep) acc[i][c] = fmaf(pw[i * KT + j], vv, acc[i][c]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+    // the warps' partial results: [VD] sums, then the maximum and the sum of weights
+    const int PW = VD + 2;
+#pragma unroll
+    for (int i = 0; i < DEC_REP; ++i) {
+        if (i < rep) {
+            float* dst = part + (warp * DEC_REP + i) * PW;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const int d = lane + 32 * c;
+                if (d < VD) dst[d] = acc[i][c];
+            }
+            if (lane == 0) {
+                dst[VD] = m[i];
+                dst[VD + 1] = l[i];
+            }
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < rep * VD; e += AWB_THREADS) {
+        const int i = e / VD, d = e - i * VD;
+        float mm = -FLT_MAX;
+        for (int w = 0; w < AWB_WARPS; ++w) mm = fmaxf(mm, part[(w * DEC_REP + i) * PW + VD]);
+        float num = 0.f, den = 0.f;
+        for (int w = 0; w < AWB_WARPS; ++w) {
+            const float* src = part + (w * DEC_REP + i) * PW;
+            const float f = expf(src[VD] - mm);          // 0 for a warp that saw no key (its maximum is -FLT_MAX)
+            num = fmaf(src[d], f, num);
+            den = fmaf(src[VD + 1], f, den);
+        }
+        out[((size_t)row * nh + h0 + i) * VD + d] = ap_from_float<TA>(num / den);
+    }
+}
+
 AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cache, int dtype, const int* block_table,
                                        int max_blocks, const int* seq_start, const int* positions, int nseq, int T,
                                        int nh, int nkv, int D, int VD, int P, long long page_stride, float scale,
-                                       int window, const float* r1, const float* r2, cudaStream_t stream) {
+                                       int window, const float* r1, const float* r2, int single_rows, int other_rows,
+                                       cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && nseq >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0 && P > 0 && max_blocks > 0,
                "attention_window_bias: bad sizes T=%d heads=%d kv_heads=%d page=%d", T, nh, nkv, P);
     AP_REQUIRE(D > 0 && VD > 0 && D <= MAX_HEAD && VD <= MAX_HEAD,
@@ -251,6 +401,33 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
     AP_REQUIRE(nh <= 65535, "attention_window_bias: %d heads exceed the grid", nh);
     AP_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attention_window_bias: the bias needs both of its tables");
     if (T == 0 || nseq == 0) return AP_OK;
+    // single_rows: sequences that bring one row go to the kernel made for them; other_rows: there are
+    // sequences with another number of rows (both 0: everything on the general kernel)
+    if (single_rows) {
+        const int rep = nh / nkv;
+        const dim3 dgrid((unsigned)nseq, (unsigned)nkv, (unsigned)((rep + DEC_REP - 1) / DEC_REP));
+        const size_t dsmem = ((size_t)DEC_REP * D + (size_t)AWB_WARPS * DEC_REP * KT +
+                              (size_t)AWB_WARPS * DEC_REP * (VD + 2)) * sizeof(float);
+        AP_REQUIRE(nkv <= 65535, "attention_window_bias: %d key/value heads exceed the grid", nkv);
+#define LAUNCH_DEC(TA)                                                                                               \
+    do {                                                                                                             \
+        auto kern = attention_window_bias_decode_kernel<TA>;                                                         \
+        if (dsmem > 48 * 1024) {                                                                                     \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsmem);     \
+            AP_REQUIRE(e == cudaSuccess, "attention_window_bias: cannot reserve %zu bytes of shared memory", dsmem); \
+        }                                                                                                            \
+        AP_CHECK_PDL_LAUNCH("attention_window_bias_decode",                                                          \
+                            ap_launch_pdl(kern, dgrid, dim3(AWB_THREADS), dsmem, stream, (const TA*)q, (TA*)out,     \
+                                          (const TA*)cache, block_table, max_blocks, seq_start, positions, nh, nkv,  \
+                                          D, VD, P, (size_t)page_stride, scale, window, r1, r2));                    \
+    } while (0)
+        if (dtype == AP_F32) LAUNCH_DEC(float);
+        else if (dtype == AP_BF16) LAUNCH_DEC(bf16);
+        else AP_REQUIRE(false, "attention_window_bias: unknown dtype %d", dtype);
+#undef LAUNCH_DEC
+        if (!other_rows) return AP_OK;
+    }
+    const int skip_single = single_rows ? 1 : 0;
     // every sequence's rows in tiles of QT: at most T / QT whole tiles and one ragged tile per sequence
     const dim3 grid((unsigned)(T / QT + nseq), (unsigned)nh);
     const size_t smem = ((size_t)QT * D + (size_t)KT * (D + 1) + (size_t)KT * VD + AWB_WARPS * RPW * KT) * sizeof(float);
@@ -264,7 +441,7 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         AP_CHECK_PDL_LAUNCH("attention_window_bias",                                                                 \
                             ap_launch_pdl(kern, grid, dim3(AWB_THREADS), smem, stream, (const TA*)q, (TA*)out,       \
                                           (const TA*)cache, block_table, max_blocks, seq_start, positions, nseq, nh, \
-                                          nkv, D, VD, P, (size_t)page_stride, scale, window, r1, r2));               \
+                                          nkv, D, VD, P, (size_t)page_stride, scale, window, r1, r2, skip_single));  \
     } while (0)
     if (dtype == AP_F32) LAUNCH(float);
     else if (dtype == AP_BF16) LAUNCH(bf16);

@@ -72,19 +72,39 @@ AP_EXPORT int ap_gated_act(const void* in, int in_dtype, void* out, int out_dtyp
 #define ROUTE_MAX_PER_LANE 8          // experts <= 256
 #define ROUTE_MAX_TOP 16
 
-// one warp per row; logits: [T, E] 32-bit (bias not yet added)
+// One warp per row.  With `rows` the warp first forms the row's router logits itself: E dot
+// products of the row with the router's rows, 32-bit sums (every lane a strided part of K, then a
+// butterfly over the lanes: one fixed order whatever the batch); else it reads them from `logits`
+// [T, E].  The bias is added, the `top` largest are taken, and their softmax is the weight.
+template <typename TA, typename TW>
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ chosen,
-                 float* __restrict__ weight, int T, int E, int top) {
+moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, const TW* __restrict__ router, int K,
+                 const float* __restrict__ bias, int* __restrict__ chosen, float* __restrict__ weight, int T, int E,
+                 int top) {
     ap_pdl_trigger();
     ap_pdl_wait();
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= T) return;
     float z[ROUTE_MAX_PER_LANE];
 #pragma unroll
-    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
-        const int e = lane + 32 * i;
-        z[i] = e < E ? logits[(size_t)t * E + e] + (bias ? bias[e] : 0.f) : -FLT_MAX;
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) z[i] = -FLT_MAX;
+    if (rows != nullptr) {
+        const TA* a = rows + (size_t)t * K;
+        for (int e = 0; e < E; ++e) {
+            const TW* w = router + (size_t)e * K;
+            float sum = 0.f;
+            for (int k = lane; k < K; k += 32) sum = fmaf(ap_to_float(a[k]), ap_to_float(w[k]), sum);
+            sum = ap_warp_sum(sum) + (bias ? bias[e] : 0.f);
+#pragma unroll
+            for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
+                if (e == lane + 32 * i) z[i] = sum;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E) z[i] = logits[(size_t)t * E + e] + (bias ? bias[e] : 0.f);
+        }
     }
     float best[ROUTE_MAX_TOP];
     int who[ROUTE_MAX_TOP];
@@ -123,8 +143,28 @@ AP_EXPORT int ap_moe_route(const float* logits, const float* bias, int* chosen, 
     AP_REQUIRE(T >= 0 && E > 0 && E <= 32 * ROUTE_MAX_PER_LANE && top > 0 && top <= E && top <= ROUTE_MAX_TOP,
                "moe_route: %d experts (at most %d), %d chosen (at most %d)", E, 32 * ROUTE_MAX_PER_LANE, top, ROUTE_MAX_TOP);
     if (T == 0) return AP_OK;
-    AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel, dim3((unsigned)((T + 3) / 4)), dim3(128), 0, stream,
-                                                   logits, bias, chosen, weight, T, E, top));
+    AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<float, float>, dim3((unsigned)((T + 3) / 4)), dim3(128),
+                                                   0, stream, logits, (const float*)nullptr, (const float*)nullptr, 0, bias,
+                                                   chosen, weight, T, E, top));
+    return AP_OK;
+}
+
+// the same from the rows themselves: rows [T, K], router [E, K]
+AP_EXPORT int ap_moe_route_rows(const void* rows, int rows_dtype, const void* router, int router_dtype, int K,
+                                const float* bias, int* chosen, float* weight, int T, int E, int top,
+                                cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && K > 0 && E > 0 && E <= 32 * ROUTE_MAX_PER_LANE && top > 0 && top <= E && top <= ROUTE_MAX_TOP,
+               "moe_route: %d experts (at most %d), %d chosen (at most %d)", E, 32 * ROUTE_MAX_PER_LANE, top, ROUTE_MAX_TOP);
+    if (T == 0) return AP_OK;
+#define LAUNCH(TA, TW)                                                                                             \
+    AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<TA, TW>, dim3((unsigned)((T + 3) / 4)), dim3(128), 0, \
+                                                   stream, (const float*)nullptr, (const TA*)rows, (const TW*)router, K, \
+                                                   bias, chosen, weight, T, E, top))
+    if (rows_dtype == AP_F32 && router_dtype == AP_F32) LAUNCH(float, float);
+    else if (rows_dtype == AP_BF16 && router_dtype == AP_BF16) LAUNCH(bf16, bf16);
+    else if (rows_dtype == AP_BF16 && router_dtype == AP_F32) LAUNCH(bf16, float);
+    else AP_REQUIRE(false, "moe_route: unsupported dtypes rows=%d router=%d", rows_dtype, router_dtype);
+#undef LAUNCH
     return AP_OK;
 }
 
@@ -135,10 +175,11 @@ AP_EXPORT int ap_moe_route(const float* logits, const float* bias, int* chosen, 
 #define SORT_MAX_EXPERTS 256
 
 // One CTA.  place[pair] = position of the pair in the grouped order; perm[position] = pair;
-// tiles[i] = (expert, first position, rows); tiles[max_tiles] holds their number in .x.
+// tiles[i] = (expert, first position, rows); tiles[max_tiles] holds their number in .x;
+// offsets[e] (optional, E + 1 entries) = first position of expert e's pairs.
 __global__ void __launch_bounds__(1024)
 moe_sort_kernel(const int* __restrict__ chosen, int* __restrict__ perm, int* __restrict__ place, int3* __restrict__ tiles,
-                int pairs, int E, int max_tiles) {
+                int* __restrict__ offsets, int pairs, int E, int max_tiles) {
     __shared__ int count[SORT_MAX_EXPERTS];
     __shared__ int first[SORT_MAX_EXPERTS + 1];
     ap_pdl_trigger();
@@ -158,6 +199,8 @@ moe_sort_kernel(const int* __restrict__ chosen, int* __restrict__ perm, int* __r
         tiles[max_tiles] = make_int3(nt, 0, 0);
     }
     __syncthreads();
+    if (offsets != nullptr)
+        for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = first[e];
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
@@ -170,11 +213,12 @@ moe_sort_kernel(const int* __restrict__ chosen, int* __restrict__ perm, int* __r
 
 AP_EXPORT int ap_moe_max_tiles(int pairs, int E) { return (pairs + MOE_BM - 1) / MOE_BM + E; }
 
-AP_EXPORT int ap_moe_sort(const int* chosen, int* perm, int* place, int* tiles, int pairs, int E, cudaStream_t stream) {
+AP_EXPORT int ap_moe_sort(const int* chosen, int* perm, int* place, int* tiles, int* offsets, int pairs, int E,
+                          cudaStream_t stream) {
     AP_REQUIRE(pairs >= 0 && E > 0 && E <= SORT_MAX_EXPERTS, "moe_sort: %d experts (at most %d)", E, SORT_MAX_EXPERTS);
     if (pairs == 0) return AP_OK;
     AP_CHECK_PDL_LAUNCH("moe_sort", ap_launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, chosen, perm, place,
-                                                  (int3*)tiles, pairs, E, ap_moe_max_tiles(pairs, E)));
+                                                  (int3*)tiles, offsets, pairs, E, ap_moe_max_tiles(pairs, E)));
     return AP_OK;
 }
 
@@ -297,6 +341,29 @@ AP_EXPORT int ap_moe_down(const void* y, int y_dtype, const void* w, int w_dtype
     else if (y_dtype == AP_BF16 && w_dtype == AP_F32) LAUNCH(bf16, float);
     else AP_REQUIRE(false, "moe_down: unsupported dtypes y=%d w=%d", y_dtype, w_dtype);
 #undef LAUNCH
+    return AP_OK;
+}
+
+// rows of `a` in grouped order: out[p, :] = a[perm[p] / top, :]   (16-bit elements, K a multiple of 8)
+__global__ void moe_gather_kernel(const uint4* __restrict__ a, uint4* __restrict__ out, const int* __restrict__ perm,
+                                  int top, int pairs, int K8) {
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    const size_t n = (size_t)pairs * K8;
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t p = e / K8, c = e - p * K8;
+        out[e] = a[(size_t)(perm[p] / top) * K8 + c];
+    }
+}
+
+AP_EXPORT int ap_moe_gather(const void* a, void* out, const int* perm, int top, int pairs, int K, cudaStream_t stream) {
+    AP_REQUIRE(pairs >= 0 && top > 0 && K > 0 && K % 8 == 0, "moe_gather: rows of %d 16-bit elements are not whole 16-byte runs", K);
+    AP_REQUIRE((((uintptr_t)a | (uintptr_t)out) & 15) == 0, "moe_gather: buffers must be 16-byte aligned");
+    if (pairs == 0) return AP_OK;
+    long long blocks = ((long long)pairs * (K / 8) + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    AP_CHECK_PDL_LAUNCH("moe_gather", ap_launch_pdl(moe_gather_kernel, dim3((unsigned)blocks), dim3(256), 0, stream,
+                                                    (const uint4*)a, (uint4*)out, perm, top, pairs, K / 8));
     return AP_OK;
 }
 

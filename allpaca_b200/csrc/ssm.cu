@@ -104,9 +104,9 @@ AP_EXPORT int ap_causal_conv_silu(const float* in, long long ld_in, int col0, co
 // whose partial sums of y meet by shuffles.  Tokens are staged through shared memory
 // SCAN_CHUNK at a time.
 #define NPT 16
-#define SCAN_CHUNK 8
+#define SCAN_CHUNK 16
 
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(128)
 ssm_scan_kernel(const float* __restrict__ xbc, long long ld_xbc,           // [T, inner + 2 G N]: x | B | C
                 const float* __restrict__ dt_raw, long long ld_dt,         // [T, .]: column h is head h
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
@@ -197,7 +197,10 @@ AP_EXPORT int ap_ssm_scan(const float* xbc, long long ld_xbc, const float* dt_ra
     while (NP * NPT < N) NP *= 2;
     // at least four lanes to a column, so that a head of few columns still fills warps
     while (NP < 4 && NP < N) NP *= 2;
-    int cols = 1024 / NP;                                     // value columns per CTA
+    // value columns per CTA: CTAs of four warps, many of them, rather than few large ones: the loop over a
+    // sequence's tokens is a chain, and what hides its latency is other chains on the same SM
+    int cols = 128 / NP;
+    if (cols < 1) cols = 1;
     if (cols > vdim) cols = vdim;
     int threads = (cols * NP + 31) / 32 * 32;
     cols = threads / NP;

@@ -43,8 +43,9 @@ _CORE_SIGNATURES = {
     #                      max_blocks, T, nh, nkv, D, VD, P, page_stride, eps, normalise, temp_coef, temp_every, stream)
     "ap_qk_norm_store": [_P, _I, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _F, _I, _P],
     # int ap_attention_window_bias(q, out, cache, dtype, block_table, max_blocks, seq_start, positions, nseq, T,
-    #                              nh, nkv, D, VD, P, page_stride, scale, window, r1, r2, stream)
-    "ap_attention_window_bias": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P, _P],
+    #                              nh, nkv, D, VD, P, page_stride, scale, window, r1, r2, single_rows, other_rows, stream)
+    "ap_attention_window_bias": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P, _I, _I,
+                                 _P],
     # int ap_causal_conv_silu(in, ld_in, col0, w, bias, state, state_stride, token_seq, seq_start, positions,
     #                         state_slots, out, T, nseq, C, taps, stream)
     "ap_causal_conv_silu": [_P, _L, _I, _P, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -56,8 +57,11 @@ _CORE_SIGNATURES = {
     # int ap_gated_act(in, in_dtype, out, out_dtype, T, I, pairs, act, limit, alpha, shift, stream)
     "ap_gated_act": [_P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P],
     "ap_moe_route": [_P, _P, _P, _P, _I, _I, _I, _P],
+    # int ap_moe_route_rows(rows, rows_dtype, router, router_dtype, K, bias, chosen, weight, T, E, top, stream)
+    "ap_moe_route_rows": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P],
     "ap_moe_max_tiles": [_I, _I],
-    "ap_moe_sort": [_P, _P, _P, _P, _I, _I, _P],
+    "ap_moe_sort": [_P, _P, _P, _P, _P, _I, _I, _P],
+    "ap_moe_gather": [_P, _P, _P, _I, _I, _I, _P],
     # int ap_moe_gate_up(a, a_dtype, w, w_dtype, y, y_dtype, perm, top, tiles, pairs, E, F, K, act, limit, alpha,
     #                    shift, stream)
     "ap_moe_gate_up": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P],

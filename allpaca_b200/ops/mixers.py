@@ -84,10 +84,16 @@ def qk_norm_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[
 def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor,
                           seq_start: torch.Tensor, positions: torch.Tensor, num_seqs: int, num_heads: int,
                           num_kv_heads: int, key_dim: int, value_dim: int, scale: float, window: int = 0,
-                          r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None) -> None:
+                          r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None,
+                          single_rows: bool = False, other_rows: bool = True) -> None:
     """Causal attention of ``q [T, nh*D]`` over pages ``[pages, nkv, P, D + VD]`` into
     ``out [T, nh*VD]``: ``score = q.k * scale - r1[h] * ln(1 + r2[h] * distance)`` (``r1``, ``r2``
-    32-bit ``[nh]`` or None), over the last ``window`` keys (0: all), ordinary softmax, 32-bit."""
+    32-bit ``[nh]`` or None), over the last ``window`` keys (0: all), ordinary softmax, 32-bit.
+
+    ``single_rows``: sequences that bring one row run on the kernel made for decoding (the query
+    heads of a key/value head together, the key tiles spread over the warps); ``other_rows`` says
+    whether the step has sequences of another length as well (they run on the general kernel,
+    which serves everything when ``single_rows`` is False)."""
     _check(q, "q", dims=2)
     _check(out, "out", q.dtype, 2)
     T = q.shape[0]
@@ -109,7 +115,8 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
     call(core(), "ap_attention_window_bias", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(), dtype_code(q.dtype),
          block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(), positions.data_ptr(), int(num_seqs), T,
          num_heads, num_kv_heads, key_dim, value_dim, P, page_stride, float(scale), int(window or 0),
-         r1.data_ptr() if r1 is not None else 0, r2.data_ptr() if r2 is not None else 0, stream_handle())
+         r1.data_ptr() if r1 is not None else 0, r2.data_ptr() if r2 is not None else 0,
+         1 if single_rows else 0, 1 if other_rows else 0, stream_handle())
 
 
 def causal_conv_silu(inp: torch.Tensor, col0: int, weight: torch.Tensor, bias: Optional[torch.Tensor],

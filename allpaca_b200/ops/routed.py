@@ -53,15 +53,38 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], chosen: torch.
          weight.data_ptr(), T, E, top, stream_handle())
 
 
+def moe_route_rows(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], chosen: torch.Tensor,
+                   weight: torch.Tensor) -> None:
+    """:func:`moe_route` with the router's product inside: the logits of row ``t`` are
+    ``router [E, K] @ rows[t]`` in 32-bit sums, plus ``bias``."""
+    _check(rows, "rows", dims=2)
+    _check(router, "router", dims=2)
+    _check(chosen, "chosen", torch.int32, 2)
+    _check(weight, "weight", torch.float32, 2)
+    T, K = rows.shape
+    E, top = router.shape[0], chosen.shape[1]
+    if router.shape[1] != K or tuple(chosen.shape) != (T, top) or tuple(weight.shape) != (T, top):
+        raise KernelError("moe_route_rows: shapes disagree")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != E:
+            raise KernelError("moe_route_rows: one bias per expert is needed")
+    call(core(), "ap_moe_route_rows", rows.data_ptr(), dtype_code(rows.dtype), router.data_ptr(),
+         dtype_code(router.dtype), K, bias.data_ptr() if bias is not None else 0, chosen.data_ptr(), weight.data_ptr(),
+         T, E, top, stream_handle())
+
+
 def moe_max_tiles(pairs: int, experts: int) -> int:
     """Row tiles the grouped products are planned for, whatever the routing."""
     return int(core().ap_moe_max_tiles(int(pairs), int(experts)))
 
 
-def moe_sort(chosen: torch.Tensor, perm: torch.Tensor, place: torch.Tensor, tiles: torch.Tensor, experts: int) -> None:
+def moe_sort(chosen: torch.Tensor, perm: torch.Tensor, place: torch.Tensor, tiles: torch.Tensor, experts: int,
+             offsets: Optional[torch.Tensor] = None) -> None:
     """Group the (row, choice) pairs of ``chosen [T, top]`` by expert: ``perm [pairs]`` lists the
     pairs in grouped order, ``place [pairs]`` is each pair's position in it, ``tiles
-    [max_tiles + 1, 3]`` the row tiles (expert, first position, rows) with their number last."""
+    [max_tiles + 1, 3]`` the row tiles (expert, first position, rows) with their number last,
+    ``offsets [experts + 1]`` (optional) the first position of every expert's pairs."""
     _check(chosen, "chosen", torch.int32, 2)
     pairs = chosen.numel()
     for t, n in ((perm, "perm"), (place, "place")):
@@ -71,8 +94,23 @@ def moe_sort(chosen: torch.Tensor, perm: torch.Tensor, place: torch.Tensor, tile
     _check(tiles, "tiles", torch.int32, 2)
     if tuple(tiles.shape) != (moe_max_tiles(pairs, experts) + 1, 3):
         raise KernelError("moe_sort: tiles must be [max_tiles + 1, 3]")
-    call(core(), "ap_moe_sort", chosen.data_ptr(), perm.data_ptr(), place.data_ptr(), tiles.data_ptr(), pairs,
-         int(experts), stream_handle())
+    if offsets is not None:
+        _check(offsets, "offsets", torch.int32, 1)
+        if offsets.shape[0] != experts + 1:
+            raise KernelError("moe_sort: offsets must have one entry per expert and one more")
+    call(core(), "ap_moe_sort", chosen.data_ptr(), perm.data_ptr(), place.data_ptr(), tiles.data_ptr(),
+         offsets.data_ptr() if offsets is not None else 0, pairs, int(experts), stream_handle())
+
+
+def moe_gather(a: torch.Tensor, out: torch.Tensor, perm: torch.Tensor, top: int) -> None:
+    """``out[p] = a[perm[p] // top]``: the rows of 16-bit ``a [T, K]`` in grouped order, ``[pairs, K]``."""
+    _check(a, "a", torch.bfloat16, 2)
+    _check(out, "out", torch.bfloat16, 2)
+    _check(perm, "perm", torch.int32, 1)
+    if out.shape[1] != a.shape[1] or out.shape[0] != a.shape[0] * top or perm.shape[0] < out.shape[0]:
+        raise KernelError("moe_gather: shapes disagree")
+    call(core(), "ap_moe_gather", a.data_ptr(), out.data_ptr(), perm.data_ptr(), int(top), out.shape[0], a.shape[1],
+         stream_handle())
 
 
 def moe_gate_up(a: torch.Tensor, w: torch.Tensor, y: torch.Tensor, perm: torch.Tensor, top: int, tiles: torch.Tensor,

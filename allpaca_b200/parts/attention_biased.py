@@ -87,6 +87,12 @@ class DistanceBiasedAttention(Mixer):
                           normalise=self.qk_norm_eps is not None, temp_coef=self.temp_coef,
                           temp_every=self.temp_every)
         out = ws.get("battn.out", (T, self.nh * self.vd), self.env.dtype)
+        # bfloat16: one-row sequences on the decode kernel (a step of such rows only is what a CUDA graph
+        # records, and every replay is again such a step); 32-bit: one kernel for all rows, so that a
+        # row has the same bits alone, in a portion and in a batch
+        lens = step.host_query_lens
+        single = self.env.dtype == torch.bfloat16 and (step.max_query_len == 1 or 1 in lens)
         ops.attention_window_bias(q, out, cache.pages, table, step.seq_start, step.positions, step.num_seqs,
-                                  self.nh, self.nkv, self.hd, self.vd, self.scale, self.window or 0, self.r1, self.r2)
+                                  self.nh, self.nkv, self.hd, self.vd, self.scale, self.window or 0, self.r1, self.r2,
+                                  single_rows=single, other_rows=step.max_query_len != 1)
         return self.o.forward(out, "battn.o", "delta")

@@ -98,18 +98,9 @@ class Linear:
         else:
             out = ws.get(buffer_name, (T, N), torch.float32 if kind == "float32" else self.env.dtype)
             target = out
-        if tc and T > 64 and nsplit > 1:
-            # up to 256 rows against few weight tiles: K slices in a cluster, as for decoding
-            ops.gemm_tc(a, self.weight, target, nsplit, reduce=True)
-        elif tc and ops.gemm_tc_prefers_pair(T, N, self.in_features):
-            ops.gemm_tc_pair(a, self.weight, target)
-        elif tc and T > 64 and ops.gemm_tc_prefers_persistent(T, N, self.in_features):
-            ops.gemm_tc_persistent(a, self.weight, target)
-        elif tc and nsplit == 1 and ops.gemm_tc_prefers_dual(T, N, self.in_features):
-            ops.gemm_tc_dual(a, self.weight, target)
-        elif tc:
-            ops.gemm_tc(a, self.weight, target, nsplit, reduce=nsplit > 1, scale=scale)
-            scale = None
+        if tc:
+            if self.tensor_core_product(a, self.weight, target, scale):
+                scale = None
         else:
             ops.gemm_simt(a, self.weight, target)
         if scale is not None:
@@ -117,6 +108,27 @@ class Linear:
         if self.bias is not None:
             ops.bias_add(target, self.bias)
         return out
+
+    @staticmethod
+    def tensor_core_product(a: torch.Tensor, w: torch.Tensor, target: torch.Tensor, scale=None) -> bool:
+        """``target[T, N] = a[T, K] @ w[N, K]^T`` in bfloat16 on the tensor cores, by the kernel that
+        suits the shape; returns whether ``scale`` was applied (only the kernel for few rows can)."""
+        T, K = a.shape
+        N = w.shape[0]
+        nsplit = ops.gemm_tc_splits(T, N, K)
+        if T > 64 and nsplit > 1:
+            # up to 256 rows against few weight tiles: K slices in a cluster, as for decoding
+            ops.gemm_tc(a, w, target, nsplit, reduce=True)
+        elif ops.gemm_tc_prefers_pair(T, N, K):
+            ops.gemm_tc_pair(a, w, target)
+        elif T > 64 and ops.gemm_tc_prefers_persistent(T, N, K):
+            ops.gemm_tc_persistent(a, w, target)
+        elif nsplit == 1 and ops.gemm_tc_prefers_dual(T, N, K):
+            ops.gemm_tc_dual(a, w, target)
+        else:
+            ops.gemm_tc(a, w, target, nsplit, reduce=nsplit > 1, scale=scale)
+            return True
+        return False
 
     def forward_gated(self, a: torch.Tensor, buffer_name: str, scale=None) -> Optional[torch.Tensor]:
         """For a weight whose rows alternate gate and up: ``silu(a W_gate^T) * (a W_up^T)`` in one

@@ -11,6 +11,13 @@ On the device the (row, choice) pairs are grouped by expert, every expert's rows
 its two products in tiles, and a last pass adds each row's weighted results in the order of
 its choices.  Counts and tiles never leave the device, so a step can be replayed from a CUDA
 graph, and a row's result does not depend on what else is in the batch.
+
+A bfloat16 step that brings a prompt portion and many pairs takes another way: the experts'
+first positions come to the host (one small copy, and the only wait on the device in the
+step), the rows are gathered in grouped order, and every expert's rows run through the
+tcgen05 products the dense layers use, one pair of launches per expert.  Such a step is never
+recorded as a CUDA graph (only steps of one row per request are), so deciding on the host
+is safe there.
 """
 from __future__ import annotations
 
@@ -20,6 +27,7 @@ import torch
 
 from .. import ops
 from .base import BuildEnv, FeedForward, PartError, WeightSpec, register
+from .linear import Linear
 
 
 @register("feed_forward", "routed_experts")
@@ -65,23 +73,47 @@ class RoutedExperts(FeedForward):
                                     for e in range(self.experts)]).contiguous()
         self.down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
 
+    #: pairs from which a prompt step's experts run on the tensor cores, one product per expert
+    TENSOR_CORE_MIN_PAIRS = 512
+
+    def _per_expert_on_tensor_cores(self, h, step, pairs: int) -> bool:
+        return (self.env.dtype == torch.bfloat16 and step is not None and step.max_query_len > 1
+                and pairs >= self.TENSOR_CORE_MIN_PAIRS and self.gate_up.dtype == torch.bfloat16
+                and self.hidden % 8 == 0 and self.inter % 8 == 0 and ops.tensor_core_gemm_available())
+
     def forward(self, h: torch.Tensor, step) -> torch.Tensor:
         T = h.shape[0]
         ws = self.env.workspace
         pairs = T * self.top
-        logits = ws.get("moe.logits", (T, self.experts), torch.float32)
-        ops.gemm_simt(h, self.router, logits)                       # 32-bit sums on the CUDA cores
         chosen = ws.get("moe.chosen", (T, self.top), torch.int32)
         weight = ws.get("moe.weight", (T, self.top), torch.float32)
-        ops.moe_route(logits, self.router_b, chosen, weight)
+        ops.moe_route_rows(h, self.router, self.router_b, chosen, weight)     # router logits in 32-bit sums
         perm = ws.get("moe.perm", (pairs,), torch.int32)
         place = ws.get("moe.place", (pairs,), torch.int32)
         tiles = ws.get("moe.tiles", (ops.moe_max_tiles(pairs, self.experts) + 1, 3), torch.int32)
-        ops.moe_sort(chosen, perm, place, tiles, self.experts)
         y = ws.get("moe.act", (pairs, self.inter), self.env.dtype)
-        ops.moe_gate_up(h, self.gate_up, y, perm, self.top, tiles, self.activation, self.limit, self.alpha, self.shift)
         o = ws.get("moe.out", (pairs, self.hidden), torch.float32)
-        ops.moe_down(y, self.down, o, tiles)
+        if self._per_expert_on_tensor_cores(h, step, pairs):
+            offsets = ws.get("moe.offsets", (self.experts + 1,), torch.int32)
+            ops.moe_sort(chosen, perm, place, tiles, self.experts, offsets)
+            first = offsets.tolist()                                   # the step waits for the device here
+            rows = ws.get("moe.rows", (pairs, self.hidden), torch.bfloat16)
+            ops.moe_gather(h, rows, perm, self.top)
+            gu = ws.get("moe.gate_up", (pairs, 2 * self.inter), torch.bfloat16)
+            for e in range(self.experts):
+                a, b = first[e], first[e + 1]
+                if b > a:
+                    Linear.tensor_core_product(rows[a:b], self.gate_up[e], gu[a:b])
+            ops.gated_act(gu, y, self.activation, False, self.limit, self.alpha, self.shift)
+            for e in range(self.experts):
+                a, b = first[e], first[e + 1]
+                if b > a:
+                    Linear.tensor_core_product(y[a:b], self.down[e], o[a:b])
+        else:
+            ops.moe_sort(chosen, perm, place, tiles, self.experts)
+            ops.moe_gate_up(h, self.gate_up, y, perm, self.top, tiles, self.activation, self.limit, self.alpha,
+                            self.shift)
+            ops.moe_down(y, self.down, o, tiles)
         delta = ws.get("moe.delta", (1, T, self.hidden), torch.float32)
         ops.moe_combine(o, place, weight, delta[0])
         return delta

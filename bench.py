@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --design viresun [--design-size small|base|wide]     (see allpaca_b200/bench_designs.py)
 
 Default run: the layer sizes of the Llama-3.1-8B shape (preset ``llama-3.1-8b``), random
 bfloat16 weights drawn on the device, 8 requests decoding at a context of 4096 tokens.
@@ -280,6 +281,10 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true", help="time only the prefill (for profilers)")
     ap.add_argument("--seed", type=int, default=2)
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profilers)")
+    ap.add_argument("--design", default=None, choices=["viresun"],
+                    help="instead of the default workload: prefill and decode of this design at layer sizes of a "
+                         "real model, beside the Llama decoder of equal size, with per-kernel times")
+    ap.add_argument("--design-size", default="base", choices=["small", "base", "wide"])
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -294,6 +299,11 @@ def main() -> int:
               f"(the steps run once through the entry point and once device-timed)", file=sys.stderr)
         return 2
 
+    if args.design:
+        from allpaca_b200 import bench_designs
+        print(json.dumps(bench_designs.run(args.design, args.design_size, min(args.steps, 64), args.warmup, args.batch,
+                                           args.context, args.prefill_tokens, peaks(), ClockSampler())))
+        return 0
     from allpaca_b200 import ops
     pk = peaks()
     max_batch = args.batch if args.no_points else max(args.batch, 128)

@@ -82,7 +82,7 @@ def run_trace(model_dir: str, dtype: str, out_dir: str, steps: List[dict], max_t
               extra: Sequence[str] = (), env=None, timeout: int = 900) -> Dict[int, np.ndarray]:
     """Run bin/trace_run as a user would and read back every file it wrote."""
     cfg = load_config(model_dir)
-    vocab = cfg["vocab_size"]
+    vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     lines = "".join(json.dumps(s) + "\n" for s in steps)
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
            "--out", out_dir, "--max-tokens", str(max_tokens), *extra]
