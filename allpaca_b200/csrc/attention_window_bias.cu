@@ -244,6 +244,222 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
 }
 
 // ---------------------------------------------------------------------------------------
+// bfloat16, sequences of several rows, head sizes up to 128: the same attention on the tensor
+// cores (mma.sync m16n8k16, 32-bit accumulators).  A CTA of four warps takes 64 consecutive rows
+// of one sequence and one query head, 16 rows to a warp, whose queries stay in registers as the
+// first product's A operand; keys come 64 at a time through shared memory ([key][d], the B
+// operand as it lies), values transposed ([d][key]) for the second product.  Scores leave the
+// first product as 32-bit sums; scale, distance bias, window and the online softmax act on them
+// in registers; the weights are rounded to bfloat16 only as the second product's A operand,
+// their sum is kept in 32-bit.  DK, DV: the head sizes rounded up to a size the kernel is
+// built for (operands are zero beyond the real sizes).
+// ---------------------------------------------------------------------------------------
+#define MQ 64
+#define MK 64
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int DK, int DV>
+__global__ void __launch_bounds__(AWB_THREADS)
+attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
+                                 const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_start,
+                                 const int* __restrict__ positions, int nseq, int nh, int nkv, int D, int VD, int P,
+                                 size_t page_stride, float scale, int window, const float* __restrict__ r1,
+                                 const float* __restrict__ r2, int skip_single) {
+    __shared__ __align__(16) bf16 k_s[MK][DK + 8];
+    __shared__ __align__(16) bf16 vt_s[DV][MK + 8];
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    int b = blockIdx.x, seq = -1, row0 = 0, nrows = 0;
+    for (int s = 0; s < nseq; ++s) {
+        const int a = seq_start[s], n = seq_start[s + 1] - a;
+        const int tiles = (skip_single && n == 1) ? 0 : (n + MQ - 1) / MQ;
+        if (b < tiles) {
+            seq = s;
+            row0 = a + b * MQ;
+            nrows = min(MQ, n - b * MQ);
+            break;
+        }
+        b -= tiles;
+    }
+    if (seq < 0) return;
+    const int h = blockIdx.y, kvh = h / (nh / nkv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int* table = block_table + (size_t)seq * max_blocks;
+    const int pos_first = positions[row0], pos_last = pos_first + nrows - 1;
+    // this warp's queries as A fragments: rows g and g + 8 of its 16
+    uint32_t qa[DK / 16][4];
+    {
+        const int ra = warp * 16 + g, rb = ra + 8;
+        const bf16* qra = q + ((size_t)(row0 + ra) * nh + h) * D;
+        const bf16* qrb = q + ((size_t)(row0 + rb) * nh + h) * D;
+        const bf16 zero = __float2bfloat16_rn(0.f);
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ++ks) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int c = ks * 16 + half * 8 + 2 * t4;
+                const bf16 a0 = (ra < nrows && c < D) ? qra[c] : zero, a1 = (ra < nrows && c + 1 < D) ? qra[c + 1] : zero;
+                const bf16 b0 = (rb < nrows && c < D) ? qrb[c] : zero, b1 = (rb < nrows && c + 1 < D) ? qrb[c + 1] : zero;
+                qa[ks][half * 2] = (uint32_t)__bfloat16_as_ushort(a0) | ((uint32_t)__bfloat16_as_ushort(a1) << 16);
+                qa[ks][half * 2 + 1] = (uint32_t)__bfloat16_as_ushort(b0) | ((uint32_t)__bfloat16_as_ushort(b1) << 16);
+            }
+        }
+    }
+    const float b1h = r1 ? r1[h] : 0.f, b2h = r2 ? r2[h] : 0.f;
+    const int klo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    float o[DV / 8][4];
+#pragma unroll
+    for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-FLT_MAX, -FLT_MAX}, l[2] = {0.f, 0.f};
+    const bool vec = D % 8 == 0 && VD % 8 == 0 && page_stride % 8 == 0 && ((uintptr_t)cache & 15) == 0;
+    const int row_a = warp * 16 + g;                        // this lane's rows: row_a and row_a + 8
+    for (int k0 = klo / MK * MK; k0 <= pos_last; k0 += MK) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < MK * (DK / 8); idx += AWB_THREADS) {
+            const int j = idx / (DK / 8), d0 = (idx - j * (DK / 8)) * 8;
+            const int kp = k0 + j;
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (kp >= klo && kp <= pos_last && d0 < D) {
+                const bf16* src = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * (D + VD) + d0;
+                if (vec) {
+                    val = *reinterpret_cast<const uint4*>(src);
+                } else {
+                    bf16* dst = reinterpret_cast<bf16*>(&val);
+                    for (int e = 0; e < 8; ++e)
+                        if (d0 + e < D) dst[e] = src[e];
+                }
+            }
+            *reinterpret_cast<uint4*>(&k_s[j][d0]) = val;
+        }
+        for (int idx = threadIdx.x; idx < MK * (DV / 8); idx += AWB_THREADS) {
+            const int j = idx % MK, d0 = (idx / MK) * 8;
+            const int kp = k0 + j;
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (kp >= klo && kp <= pos_last && d0 < VD) {
+                const bf16* src = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * (D + VD) + D + d0;
+                if (vec) {
+                    val = *reinterpret_cast<const uint4*>(src);
+                } else {
+                    bf16* dst = reinterpret_cast<bf16*>(&val);
+                    for (int e = 0; e < 8; ++e)
+                        if (d0 + e < VD) dst[e] = src[e];
+                }
+            }
+            const bf16* ve = reinterpret_cast<const bf16*>(&val);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) vt_s[d0 + e][j] = ve[e];
+        }
+        __syncthreads();
+        if (warp * 16 >= nrows) continue;                   // this warp has no rows (it helped loading)
+        float sc[MK / 8][4];
+#pragma unroll
+        for (int nb = 0; nb < MK / 8; ++nb) sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < DK / 16; ++ks) {
+#pragma unroll
+            for (int nb = 0; nb < MK / 8; ++nb) {
+                const uint32_t kb0 = *reinterpret_cast<const uint32_t*>(&k_s[nb * 8 + g][ks * 16 + 2 * t4]);
+                const uint32_t kb1 = *reinterpret_cast<const uint32_t*>(&k_s[nb * 8 + g][ks * 16 + 8 + 2 * t4]);
+                mma_bf16_16816(sc[nb], qa[ks], kb0, kb1);
+            }
+        }
+        // scale, bias, window; the tile's row maxima
+        float mx[2] = {-FLT_MAX, -FLT_MAX};
+#pragma unroll
+        for (int nb = 0; nb < MK / 8; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = row_a + (e >> 1) * 8;
+                const int dist = pos_first + r - (k0 + nb * 8 + 2 * t4 + (e & 1));
+                const bool seen = r < nrows && dist >= 0 && (window <= 0 || dist < window);
+                const float v = seen ? sc[nb][e] * scale - b1h * log1pf(b2h * (float)dist) : -FLT_MAX;
+                sc[nb][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+        float alpha[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float m_new = fmaxf(m[i], mx[i]);
+            alpha[i] = expf(m[i] - m_new);
+            m[i] = m_new;
+            l[i] *= alpha[i];
+        }
+#pragma unroll
+        for (int nb = 0; nb < MK / 8; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float p = sc[nb][e] > -FLT_MAX ? expf(sc[nb][e] - m[e >> 1]) : 0.f;
+                sc[nb][e] = p;
+                l[e >> 1] += p;                              // this lane's share; the quad's shares meet at the end
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < DV / 8; ++i) {
+            o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+            o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        }
+#pragma unroll
+        for (int kb = 0; kb < MK / 16; ++kb) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(sc[2 * kb][0], sc[2 * kb][1]);
+            pa[1] = pack_bf16(sc[2 * kb][2], sc[2 * kb][3]);
+            pa[2] = pack_bf16(sc[2 * kb + 1][0], sc[2 * kb + 1][1]);
+            pa[3] = pack_bf16(sc[2 * kb + 1][2], sc[2 * kb + 1][3]);
+#pragma unroll
+            for (int nb = 0; nb < DV / 8; ++nb) {
+                const uint32_t vb0 = *reinterpret_cast<const uint32_t*>(&vt_s[nb * 8 + g][kb * 16 + 2 * t4]);
+                const uint32_t vb1 = *reinterpret_cast<const uint32_t*>(&vt_s[nb * 8 + g][kb * 16 + 8 + 2 * t4]);
+                mma_bf16_16816(o[nb], pa, vb0, vb1);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = row_a + i * 8;
+        if (r >= nrows) continue;
+        const float inv = 1.0f / l[i];
+        bf16* dst = out + ((size_t)(row0 + r) * nh + h) * VD;
+#pragma unroll
+        for (int nb = 0; nb < DV / 8; ++nb) {
+            const int c = nb * 8 + 2 * t4;
+            if (c < VD) dst[c] = __float2bfloat16_rn(o[nb][2 * i] * inv);
+            if (c + 1 < VD) dst[c + 1] = __float2bfloat16_rn(o[nb][2 * i + 1] * inv);
+        }
+    }
+}
+
+template <int DK, int DV>
+static int launch_awb_mma(const void* q, void* out, const void* cache, const int* block_table, int max_blocks,
+                          const int* seq_start, const int* positions, int nseq, int T, int nh, int nkv, int D, int VD,
+                          int P, long long page_stride, float scale, int window, const float* r1, const float* r2,
+                          int skip_single, cudaStream_t stream) {
+    const dim3 grid((unsigned)(T / MQ + nseq), (unsigned)nh);
+    AP_CHECK_PDL_LAUNCH("attention_window_bias_mma",
+                        ap_launch_pdl(attention_window_bias_mma_kernel<DK, DV>, grid, dim3(AWB_THREADS), 0, stream,
+                                      (const bf16*)q, (bf16*)out, (const bf16*)cache, block_table, max_blocks, seq_start,
+                                      positions, nseq, nh, nkv, D, VD, P, (size_t)page_stride, scale, window, r1, r2,
+                                      skip_single));
+    return AP_OK;
+}
+
+// ---------------------------------------------------------------------------------------
 // Sequences that bring one row (decoding).  One CTA per (sequence, key/value head): the query
 // heads that share the key/value head are served together, so every key and value is read
 // once for all of them.  The four warps take the key tiles in turn (tile i goes to warp
@@ -275,6 +491,8 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
     float* q_s = smem;                                   // [DEC_REP][D]
     float* p_s = q_s + DEC_REP * D;                      // [AWB_WARPS][DEC_REP][KT]
     float* part = p_s + AWB_WARPS * DEC_REP * KT;        // [AWB_WARPS][DEC_REP][VD + 2]
+    const int VDP = (VD + 7) / 8 * 8;                    // a value row in shared memory, padded to 16-byte runs
+    TA* v_s = reinterpret_cast<TA*>(part + AWB_WARPS * DEC_REP * (VD + 2)) + (size_t)warp * KT * VDP;   // [KT][VDP] per warp
     for (int i = threadIdx.x; i < rep * D; i += AWB_THREADS)
         q_s[i] = ap_to_float(q[((size_t)row * nh + h0) * D + i]);
     __syncthreads();
@@ -305,6 +523,7 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
             if (sizeof(TA) == 2 && D % 8 == 0 && (D + VD) % 8 == 0 && (page_stride % 8) == 0 &&
                 ((uintptr_t)cache & 15) == 0) {
                 // eight 16-bit elements of the key's row per load
+#pragma unroll 4
                 for (int d = 0; d < D; d += 8) {
                     const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(kr) + d);
                     const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -338,11 +557,24 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
 #pragma unroll
             for (int c = 0; c < NC; ++c) acc[i][c] *= alpha;
         }
+        // every lane brings its key's value row into the warp's tile (all loads of a lane in flight at once)
+        if (seen) {
+            const TA* vr = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * (D + VD) + D;
+            TA* dst = v_s + lane * VDP;
+            if (sizeof(TA) == 2 && D % 8 == 0 && VD % 8 == 0 && (page_stride % 8) == 0 && ((uintptr_t)cache & 15) == 0) {
+#pragma unroll 4
+                for (int d = 0; d < VD; d += 8)
+                    *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + d) =
+                        *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(vr) + d);
+            } else {
+#pragma unroll 4
+                for (int d = 0; d < VD; ++d) dst[d] = vr[d];
+            }
+        }
         __syncwarp();
         const int last = min(KT, qpos - tile * KT + 1);
         for (int j = max(0, klo - tile * KT); j < last; ++j) {
-            const int kj = tile * KT + j;
-            const TA* vr = cache + (size_t)table[kj / P] * page_stride + ((size_t)kvh * P + kj % P) * (D + VD) + D;
+            const TA* vr = v_s + j * VDP;
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
                 if (c < nc) {
@@ -407,7 +639,8 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         const int rep = nh / nkv;
         const dim3 dgrid((unsigned)nseq, (unsigned)nkv, (unsigned)((rep + DEC_REP - 1) / DEC_REP));
         const size_t dsmem = ((size_t)DEC_REP * D + (size_t)AWB_WARPS * DEC_REP * KT +
-                              (size_t)AWB_WARPS * DEC_REP * (VD + 2)) * sizeof(float);
+                              (size_t)AWB_WARPS * DEC_REP * (VD + 2)) * sizeof(float) +
+                             (size_t)AWB_WARPS * KT * ((VD + 7) / 8 * 8) * (dtype == AP_F32 ? 4 : 2) + 16;
         AP_REQUIRE(nkv <= 65535, "attention_window_bias: %d key/value heads exceed the grid", nkv);
 #define LAUNCH_DEC(TA)                                                                                               \
     do {                                                                                                             \
@@ -428,6 +661,24 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         if (!other_rows) return AP_OK;
     }
     const int skip_single = single_rows ? 1 : 0;
+    if (dtype == AP_BF16 && D <= 128 && VD <= 128) {
+        // the tensor-core kernel, built for head sizes rounded up to 32, 64 or 128
+        const int dk = D <= 32 ? 32 : (D <= 64 ? 64 : 128), dv = VD <= 32 ? 32 : (VD <= 64 ? 64 : 128);
+#define MMA_ARGS q, out, cache, block_table, max_blocks, seq_start, positions, nseq, T, nh, nkv, D, VD, P, page_stride, \
+                 scale, window, r1, r2, skip_single, stream
+        switch (dk * 1000 + dv) {
+            case 32032: return launch_awb_mma<32, 32>(MMA_ARGS);
+            case 32064: return launch_awb_mma<32, 64>(MMA_ARGS);
+            case 32128: return launch_awb_mma<32, 128>(MMA_ARGS);
+            case 64032: return launch_awb_mma<64, 32>(MMA_ARGS);
+            case 64064: return launch_awb_mma<64, 64>(MMA_ARGS);
+            case 64128: return launch_awb_mma<64, 128>(MMA_ARGS);
+            case 128032: return launch_awb_mma<128, 32>(MMA_ARGS);
+            case 128064: return launch_awb_mma<128, 64>(MMA_ARGS);
+            default: return launch_awb_mma<128, 128>(MMA_ARGS);
+        }
+#undef MMA_ARGS
+    }
     // every sequence's rows in tiles of QT: at most T / QT whole tiles and one ragged tile per sequence
     const dim3 grid((unsigned)(T / QT + nseq), (unsigned)nh);
     const size_t smem = ((size_t)QT * D + (size_t)KT * (D + 1) + (size_t)KT * VD + AWB_WARPS * RPW * KT) * sizeof(float);

@@ -72,39 +72,55 @@ AP_EXPORT int ap_gated_act(const void* in, int in_dtype, void* out, int out_dtyp
 #define ROUTE_MAX_PER_LANE 8          // experts <= 256
 #define ROUTE_MAX_TOP 16
 
-// One warp per row.  With `rows` the warp first forms the row's router logits itself: E dot
-// products of the row with the router's rows, 32-bit sums (every lane a strided part of K, then a
-// butterfly over the lanes: one fixed order whatever the batch); else it reads them from `logits`
-// [T, E].  The bias is added, the `top` largest are taken, and their softmax is the weight.
+// One CTA of four warps per row.  With `rows` the warps first form the row's router logits: E dot
+// products of the row with the router's rows, the experts dealt to the warps in turn, 32-bit sums
+// (every lane a strided part of K, 16-byte loads where the types and alignment allow, then a
+// butterfly over the lanes: one fixed order whatever the batch); else the logits are read from
+// `logits` [T, E].  The bias is added; the first warp takes the `top` largest and their softmax.
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, const TW* __restrict__ router, int K,
                  const float* __restrict__ bias, int* __restrict__ chosen, float* __restrict__ weight, int T, int E,
                  int top) {
+    __shared__ float z_s[32 * ROUTE_MAX_PER_LANE];
     ap_pdl_trigger();
     ap_pdl_wait();
-    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (t >= T) return;
-    float z[ROUTE_MAX_PER_LANE];
-#pragma unroll
-    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) z[i] = -FLT_MAX;
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (rows != nullptr) {
         const TA* a = rows + (size_t)t * K;
-        for (int e = 0; e < E; ++e) {
+        const bool vec = sizeof(TA) == 2 && sizeof(TW) == 2 && K % 8 == 0 &&
+                         ((((uintptr_t)rows) | ((uintptr_t)router)) & 15) == 0;
+        for (int e = warp; e < E; e += 4) {
             const TW* w = router + (size_t)e * K;
             float sum = 0.f;
-            for (int k = lane; k < K; k += 32) sum = fmaf(ap_to_float(a[k]), ap_to_float(w[k]), sum);
-            sum = ap_warp_sum(sum) + (bias ? bias[e] : 0.f);
+            if (vec) {
+                for (int k = lane * 8; k < K; k += 256) {
+                    const uint4 av = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a) + k);
+                    const uint4 wv = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(w) + k);
+                    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+                    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
 #pragma unroll
-            for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
-                if (e == lane + 32 * i) z[i] = sum;
+                    for (int q = 0; q < 4; ++q) {
+                        const float2 x = __bfloat1622float2(a2[q]), y = __bfloat1622float2(w2[q]);
+                        sum = fmaf(x.y, y.y, fmaf(x.x, y.x, sum));
+                    }
+                }
+            } else {
+                for (int k = lane; k < K; k += 32) sum = fmaf(ap_to_float(a[k]), ap_to_float(w[k]), sum);
+            }
+            sum = ap_warp_sum(sum);
+            if (lane == 0) z_s[e] = sum + (bias ? bias[e] : 0.f);
         }
     } else {
+        for (int e = threadIdx.x; e < E; e += 128) z_s[e] = logits[(size_t)t * E + e] + (bias ? bias[e] : 0.f);
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float z[ROUTE_MAX_PER_LANE];
 #pragma unroll
-        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
-            const int e = lane + 32 * i;
-            if (e < E) z[i] = logits[(size_t)t * E + e] + (bias ? bias[e] : 0.f);
-        }
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        z[i] = e < E ? z_s[e] : -FLT_MAX;
     }
     float best[ROUTE_MAX_TOP];
     int who[ROUTE_MAX_TOP];
@@ -143,7 +159,7 @@ AP_EXPORT int ap_moe_route(const float* logits, const float* bias, int* chosen, 
     AP_REQUIRE(T >= 0 && E > 0 && E <= 32 * ROUTE_MAX_PER_LANE && top > 0 && top <= E && top <= ROUTE_MAX_TOP,
                "moe_route: %d experts (at most %d), %d chosen (at most %d)", E, 32 * ROUTE_MAX_PER_LANE, top, ROUTE_MAX_TOP);
     if (T == 0) return AP_OK;
-    AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<float, float>, dim3((unsigned)((T + 3) / 4)), dim3(128),
+    AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<float, float>, dim3((unsigned)T), dim3(128),
                                                    0, stream, logits, (const float*)nullptr, (const float*)nullptr, 0, bias,
                                                    chosen, weight, T, E, top));
     return AP_OK;
@@ -157,7 +173,7 @@ AP_EXPORT int ap_moe_route_rows(const void* rows, int rows_dtype, const void* ro
                "moe_route: %d experts (at most %d), %d chosen (at most %d)", E, 32 * ROUTE_MAX_PER_LANE, top, ROUTE_MAX_TOP);
     if (T == 0) return AP_OK;
 #define LAUNCH(TA, TW)                                                                                             \
-    AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<TA, TW>, dim3((unsigned)((T + 3) / 4)), dim3(128), 0, \
+    AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<TA, TW>, dim3((unsigned)T), dim3(128), 0, \
                                                    stream, (const float*)nullptr, (const TA*)rows, (const TW*)router, K, \
                                                    bias, chosen, weight, T, E, top))
     if (rows_dtype == AP_F32 && router_dtype == AP_F32) LAUNCH(float, float);

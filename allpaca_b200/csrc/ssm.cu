@@ -99,12 +99,22 @@ AP_EXPORT int ap_causal_conv_silu(const float* in, long long ld_in, int col0, co
 }
 
 // ---- the recurrence ---------------------------------------------------------------------
-// One CTA per (sequence, head).  A thread holds NPT state entries of one value column: the
-// column's N entries are spread over NP neighbouring lanes (NP a power of two up to 32),
-// whose partial sums of y meet by shuffles.  Tokens are staged through shared memory
-// SCAN_CHUNK at a time.
+// One CTA per (sequence, head, block of value columns).  A thread holds NPT state entries of one
+// value column: the column's N entries are spread over NP neighbouring lanes (NP a power of two
+// up to 32), whose partial sums of y meet by shuffles.  Tokens come SCAN_CHUNK at a time through
+// two shared-memory buffers filled by asynchronous copies: while one chunk is computed the next
+// one is on its way, so the chain over the tokens never waits for memory.
 #define NPT 16
 #define SCAN_CHUNK 16
+
+__device__ __forceinline__ void scan_copy4(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void scan_copy16(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
 
 __global__ void __launch_bounds__(128)
 ssm_scan_kernel(const float* __restrict__ xbc, long long ld_xbc,           // [T, inner + 2 G N]: x | B | C
@@ -113,8 +123,8 @@ ssm_scan_kernel(const float* __restrict__ xbc, long long ld_xbc,           // [T
                 float* __restrict__ state, long long state_stride,         // [slots][heads][N][vdim]
                 const int* __restrict__ seq_start, const int* __restrict__ positions,
                 const int* __restrict__ state_slots, float* __restrict__ y, // [T, inner]
-                int heads, int groups, int N, int vdim, int NP) {
-    extern __shared__ float sm[];
+                int heads, int groups, int N, int vdim, int NP, int cols, int vec) {
+    extern __shared__ __align__(16) float sm[];
     ap_pdl_trigger();
     ap_pdl_wait();
     const int s = blockIdx.x, h = blockIdx.y;
@@ -122,12 +132,14 @@ ssm_scan_kernel(const float* __restrict__ xbc, long long ld_xbc,           // [T
     if (n <= 0) return;
     const int g = h / (heads / groups);
     const int inner = heads * vdim;
-    const int v = blockIdx.z * (blockDim.x / NP) + threadIdx.x / NP, part = threadIdx.x % NP;
-    const bool live = v < vdim;
-    float* x_s = sm;                               // [CHUNK][vdim]
-    float* b_s = x_s + SCAN_CHUNK * vdim;          // [CHUNK][N]
-    float* c_s = b_s + SCAN_CHUNK * N;             // [CHUNK][N]
-    float* dt_s = c_s + SCAN_CHUNK * N;            // [CHUNK] step size, then [CHUNK] decay
+    const int col0 = blockIdx.z * cols;                      // first value column of this CTA
+    const int ncols = min(cols, vdim - col0);
+    const int vl = threadIdx.x / NP, part = threadIdx.x % NP;
+    const int v = col0 + vl;
+    const bool live = vl < ncols;
+    // one buffer: x [CHUNK][cols], B [CHUNK][N], C [CHUNK][N], dt [CHUNK] (raw, then the step size), decay [CHUNK]
+    const int XS = (cols + 3) / 4 * 4, NS = (N + 3) / 4 * 4;
+    const int buf_floats = SCAN_CHUNK * (XS + 2 * NS) + 2 * SCAN_CHUNK;
     float* st = state + (size_t)state_slots[s] * state_stride + (size_t)h * N * vdim;
     const bool fresh = positions[a] == 0;
     float S[NPT];
@@ -139,41 +151,80 @@ ssm_scan_kernel(const float* __restrict__ xbc, long long ld_xbc,           // [T
     const float neg_a = -expf(a_log[h]);
     const float bias = dt_bias ? dt_bias[h] : 0.f;
     const float dskip = d_skip ? d_skip[h] : 0.f;
-    for (int t0 = 0; t0 < n; t0 += SCAN_CHUNK) {
+
+    auto stage = [&](int t0, float* buf) {
         const int cnt = min(SCAN_CHUNK, n - t0);
+        float* x_b = buf;
+        float* b_b = x_b + SCAN_CHUNK * XS;
+        float* c_b = b_b + SCAN_CHUNK * NS;
+        float* dt_b = c_b + SCAN_CHUNK * NS;
+        if (vec) {
+            const int x4 = ncols / 4, n4 = N / 4;
+            for (int i = threadIdx.x; i < cnt * x4; i += blockDim.x) {
+                const int r = i / x4, d = (i - r * x4) * 4;
+                scan_copy16(x_b + r * XS + d, xbc + (size_t)(a + t0 + r) * ld_xbc + (size_t)h * vdim + col0 + d);
+            }
+            for (int i = threadIdx.x; i < cnt * n4 * 2; i += blockDim.x) {
+                const int which = i / (cnt * n4), j = i - which * cnt * n4;
+                const int r = j / n4, d = (j - r * n4) * 4;
+                scan_copy16((which ? c_b : b_b) + r * NS + d,
+                            xbc + (size_t)(a + t0 + r) * ld_xbc + inner + (size_t)(which * groups + g) * N + d);
+            }
+        } else {
+            for (int i = threadIdx.x; i < cnt * ncols; i += blockDim.x) {
+                const int r = i / ncols, d = i - r * ncols;
+                scan_copy4(x_b + r * XS + d, xbc + (size_t)(a + t0 + r) * ld_xbc + (size_t)h * vdim + col0 + d);
+            }
+            for (int i = threadIdx.x; i < cnt * N * 2; i += blockDim.x) {
+                const int which = i / (cnt * N), j = i - which * cnt * N;
+                const int r = j / N, d = j - r * N;
+                scan_copy4((which ? c_b : b_b) + r * NS + d,
+                           xbc + (size_t)(a + t0 + r) * ld_xbc + inner + (size_t)(which * groups + g) * N + d);
+            }
+        }
+        if (threadIdx.x < cnt) scan_copy4(dt_b + threadIdx.x, dt_raw + (size_t)(a + t0 + threadIdx.x) * ld_dt + h);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    stage(0, sm);
+    int which_buf = 0;
+    for (int t0 = 0; t0 < n; t0 += SCAN_CHUNK, which_buf ^= 1) {
+        const int cnt = min(SCAN_CHUNK, n - t0);
+        float* buf = sm + which_buf * buf_floats;
+        if (t0 + SCAN_CHUNK < n) {
+            stage(t0 + SCAN_CHUNK, sm + (which_buf ^ 1) * buf_floats);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
         __syncthreads();
-        for (int i = threadIdx.x; i < cnt * vdim; i += blockDim.x) {
-            const int r = i / vdim, d = i - r * vdim;
-            x_s[r * vdim + d] = xbc[(size_t)(a + t0 + r) * ld_xbc + (size_t)h * vdim + d];
-        }
-        for (int i = threadIdx.x; i < cnt * N; i += blockDim.x) {
-            const int r = i / N, d = i - r * N;
-            const float* row = xbc + (size_t)(a + t0 + r) * ld_xbc + inner + (size_t)g * N;
-            b_s[r * N + d] = row[d];
-            c_s[r * N + d] = row[(size_t)groups * N + d];
-        }
+        float* x_s = buf;
+        float* b_s = x_s + SCAN_CHUNK * XS;
+        float* c_s = b_s + SCAN_CHUNK * NS;
+        float* dt_s = c_s + SCAN_CHUNK * NS;
         if (threadIdx.x < cnt) {
-            const float dtv = ssm_softplus(dt_raw[(size_t)(a + t0 + threadIdx.x) * ld_dt + h] + bias);
+            const float dtv = ssm_softplus(dt_s[threadIdx.x] + bias);
             dt_s[threadIdx.x] = dtv;
             dt_s[SCAN_CHUNK + threadIdx.x] = expf(neg_a * dtv);
         }
         __syncthreads();
         for (int r = 0; r < cnt; ++r) {
             const float dtv = dt_s[r], decay = dt_s[SCAN_CHUNK + r];
-            const float xv = live ? x_s[r * vdim + v] : 0.f;
+            const float xv = live ? x_s[r * XS + vl] : 0.f;
             const float dx = dtv * xv;
             float acc = 0.f;
 #pragma unroll
             for (int i = 0; i < NPT; ++i) {
                 const int nn = part + i * NP;
                 if (nn < N) {
-                    S[i] = fmaf(decay, S[i], dx * b_s[r * N + nn]);
-                    acc = fmaf(S[i], c_s[r * N + nn], acc);
+                    S[i] = fmaf(decay, S[i], dx * b_s[r * NS + nn]);
+                    acc = fmaf(S[i], c_s[r * NS + nn], acc);
                 }
             }
             for (int o = NP >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (live && part == 0) y[(size_t)(a + t0 + r) * inner + (size_t)h * vdim + v] = fmaf(dskip, xv, acc);
         }
+        __syncthreads();                                     // this buffer is filled again two chunks on
     }
     if (live) {
 #pragma unroll
@@ -204,12 +255,20 @@ AP_EXPORT int ap_ssm_scan(const float* xbc, long long ld_xbc, const float* dt_ra
     if (cols > vdim) cols = vdim;
     int threads = (cols * NP + 31) / 32 * 32;
     cols = threads / NP;
+    if (cols >= 4) cols = cols / 4 * 4;                     // whole 16-byte runs of x per CTA
     const dim3 grid((unsigned)nseq, (unsigned)heads, (unsigned)((vdim + cols - 1) / cols));
-    const size_t smem = ((size_t)SCAN_CHUNK * (vdim + 2 * N) + 2 * SCAN_CHUNK) * sizeof(float);
-    AP_REQUIRE(smem <= 48 * 1024, "ssm_scan: state %d and value size %d do not fit the staging buffer", N, vdim);
+    // 16-byte copies where every run starts on a 16-byte boundary
+    const int vec = (cols % 4 == 0 && vdim % 4 == 0 && N % 4 == 0 && ld_xbc % 4 == 0 && ((uintptr_t)xbc & 15) == 0 &&
+                     (heads * vdim) % 4 == 0) ? 1 : 0;
+    const size_t smem = 2 * ((size_t)SCAN_CHUNK * ((cols + 3) / 4 * 4 + 2 * ((N + 3) / 4 * 4)) + 2 * SCAN_CHUNK) * sizeof(float);
+    if (smem > 48 * 1024) {
+        AP_REQUIRE(smem <= 200 * 1024, "ssm_scan: a state of %d entries does not fit the staging buffers", N);
+        cudaError_t e = cudaFuncSetAttribute(ssm_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        AP_REQUIRE(e == cudaSuccess, "ssm_scan: cannot reserve %zu bytes of shared memory", smem);
+    }
     AP_CHECK_PDL_LAUNCH("ssm_scan", ap_launch_pdl(ssm_scan_kernel, grid, dim3(threads), smem, stream, xbc, ld_xbc, dt_raw,
                                                   ld_dt, dt_bias, a_log, d_skip, state, state_stride, seq_start,
-                                                  positions, state_slots, y, heads, groups, N, vdim, NP));
+                                                  positions, state_slots, y, heads, groups, N, vdim, NP, cols, vec));
     return AP_OK;
 }
 
