@@ -256,6 +256,7 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
 // ---------------------------------------------------------------------------------------
 #define MQ 64
 #define MK 64
+#define MMA_BIAS_TABLE 2048      // distances the bias is tabulated for per CTA (beyond: computed in place)
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -276,6 +277,7 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
                                  const float* __restrict__ r2, int skip_single) {
     __shared__ __align__(16) bf16 k_s[MK][DK + 8];
     __shared__ __align__(16) bf16 vt_s[DV][MK + 8];
+    __shared__ float bias_s[MMA_BIAS_TABLE];               // r1 ln(1 + r2 d) for the distances this CTA meets
     ap_pdl_trigger();
     ap_pdl_wait();
     int b = blockIdx.x, seq = -1, row0 = 0, nrows = 0;
@@ -316,6 +318,11 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
     }
     const float b1h = r1 ? r1[h] : 0.f, b2h = r2 ? r2[h] : 0.f;
     const int klo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    // the largest distance any row of this CTA has to a key it may see
+    const int span = pos_last - klo + 1;
+    const bool tabled = r1 != nullptr && span <= MMA_BIAS_TABLE;
+    if (tabled)
+        for (int d = threadIdx.x; d < span; d += AWB_THREADS) bias_s[d] = b1h * log1pf(b2h * (float)d);
     float o[DV / 8][4];
 #pragma unroll
     for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -381,7 +388,8 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
                 const int r = row_a + (e >> 1) * 8;
                 const int dist = pos_first + r - (k0 + nb * 8 + 2 * t4 + (e & 1));
                 const bool seen = r < nrows && dist >= 0 && (window <= 0 || dist < window);
-                const float v = seen ? sc[nb][e] * scale - b1h * log1pf(b2h * (float)dist) : -FLT_MAX;
+                float v = -FLT_MAX;
+                if (seen) v = sc[nb][e] * scale - (tabled ? bias_s[dist] : b1h * log1pf(b2h * (float)dist));
                 sc[nb][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }
@@ -392,7 +400,7 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
             mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
             mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
             const float m_new = fmaxf(m[i], mx[i]);
-            alpha[i] = expf(m[i] - m_new);
+            alpha[i] = __expf(m[i] - m_new);
             m[i] = m_new;
             l[i] *= alpha[i];
         }
@@ -400,7 +408,8 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
         for (int nb = 0; nb < MK / 8; ++nb) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float p = sc[nb][e] > -FLT_MAX ? expf(sc[nb][e] - m[e >> 1]) : 0.f;
+                // the weight is rounded to bfloat16 for the second product: the fast exponential's error is far below that
+                const float p = sc[nb][e] > -FLT_MAX ? __expf(sc[nb][e] - m[e >> 1]) : 0.f;
                 sc[nb][e] = p;
                 l[e >> 1] += p;                              // this lane's share; the quad's shares meet at the end
             }
@@ -468,15 +477,16 @@ static int launch_awb_mma(const void* q, void* out, const void* cache, const int
 // partial results meet in shared memory and are merged in warp order.  Sequences with
 // another number of rows are left to the kernel above (`skip_single` there).
 // ---------------------------------------------------------------------------------------
-#define DEC_REP 8                 // query heads per CTA at most (more: the grid's z walks them)
+#define DEC_REP_MAX 8             // query heads per CTA at most (more: the grid's z walks them)
 
-template <typename TA>
+template <typename TA, int DEC_REP>   // DEC_REP: query heads per CTA this kernel is built for (1, 2, 4, 8)
 __global__ void __launch_bounds__(AWB_THREADS)
 attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ out, const TA* __restrict__ cache,
                                     const int* __restrict__ block_table, int max_blocks,
                                     const int* __restrict__ seq_start, const int* __restrict__ positions, int nh,
                                     int nkv, int D, int VD, int P, size_t page_stride, float scale, int window,
                                     const float* __restrict__ r1, const float* __restrict__ r2) {
+    constexpr int rep_chunk = DEC_REP;
     extern __shared__ __align__(16) float smem[];
     ap_pdl_trigger();
     ap_pdl_wait();
@@ -484,15 +494,16 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
     const int row = seq_start[seq];
     if (seq_start[seq + 1] - row != 1) return;
     const int rep_all = nh / nkv;
-    const int h0 = kvh * rep_all + blockIdx.z * DEC_REP;
-    const int rep = min(DEC_REP, rep_all - (int)blockIdx.z * DEC_REP);
+    const int h0 = kvh * rep_all + blockIdx.z * rep_chunk;      // rep_chunk <= DEC_REP query heads per CTA
+    const int rep = min(rep_chunk, rep_all - (int)blockIdx.z * rep_chunk);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int NC = MAX_HEAD / 32;
     float* q_s = smem;                                   // [DEC_REP][D]
     float* p_s = q_s + DEC_REP * D;                      // [AWB_WARPS][DEC_REP][KT]
     float* part = p_s + AWB_WARPS * DEC_REP * KT;        // [AWB_WARPS][DEC_REP][VD + 2]
     const int VDP = (VD + 7) / 8 * 8;                    // a value row in shared memory, padded to 16-byte runs
-    TA* v_s = reinterpret_cast<TA*>(part + AWB_WARPS * DEC_REP * (VD + 2)) + (size_t)warp * KT * VDP;   // [KT][VDP] per warp
+    TA* v_s = reinterpret_cast<TA*>(smem + ((DEC_REP * D + AWB_WARPS * DEC_REP * KT + AWB_WARPS * DEC_REP * (VD + 2) + 3) / 4) * 4) +
+              (size_t)warp * KT * VDP;                       // [KT][VDP] per warp, on a 16-byte boundary
     for (int i = threadIdx.x; i < rep * D; i += AWB_THREADS)
         q_s[i] = ap_to_float(q[((size_t)row * nh + h0) * D + i]);
     __syncthreads();
@@ -637,14 +648,22 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
     // sequences with another number of rows (both 0: everything on the general kernel)
     if (single_rows) {
         const int rep = nh / nkv;
-        const dim3 dgrid((unsigned)nseq, (unsigned)nkv, (unsigned)((rep + DEC_REP - 1) / DEC_REP));
-        const size_t dsmem = ((size_t)DEC_REP * D + (size_t)AWB_WARPS * DEC_REP * KT +
-                              (size_t)AWB_WARPS * DEC_REP * (VD + 2)) * sizeof(float) +
+        // all query heads of a key/value head in one CTA (every key read once) where that still fills the
+        // GPU; else fewer heads per CTA and the keys read again from L2
+        int rep_chunk = 1;
+        while (rep_chunk < DEC_REP_MAX && rep_chunk < rep) rep_chunk *= 2;
+        while (rep_chunk > 1 && (long long)nseq * nkv * ((rep + rep_chunk - 1) / rep_chunk) < 2 * 148) rep_chunk /= 2;
+        const dim3 dgrid((unsigned)nseq, (unsigned)nkv, (unsigned)((rep + rep_chunk - 1) / rep_chunk));
+        const size_t dsmem = ((size_t)rep_chunk * D + (size_t)AWB_WARPS * rep_chunk * KT +
+                              (size_t)AWB_WARPS * rep_chunk * (VD + 2)) * sizeof(float) +
                              (size_t)AWB_WARPS * KT * ((VD + 7) / 8 * 8) * (dtype == AP_F32 ? 4 : 2) + 16;
         AP_REQUIRE(nkv <= 65535, "attention_window_bias: %d key/value heads exceed the grid", nkv);
 #define LAUNCH_DEC(TA)                                                                                               \
     do {                                                                                                             \
-        auto kern = attention_window_bias_decode_kernel<TA>;                                                         \
+        auto kern = rep_chunk == 1 ? attention_window_bias_decode_kernel<TA, 1>                                      \
+                  : rep_chunk == 2 ? attention_window_bias_decode_kernel<TA, 2>                                      \
+                  : rep_chunk == 4 ? attention_window_bias_decode_kernel<TA, 4>                                      \
+                                   : attention_window_bias_decode_kernel<TA, 8>;                                     \
         if (dsmem > 48 * 1024) {                                                                                     \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsmem);     \
             AP_REQUIRE(e == cudaSuccess, "attention_window_bias: cannot reserve %zu bytes of shared memory", dsmem); \

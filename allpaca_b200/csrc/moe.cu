@@ -317,6 +317,107 @@ moe_gemm_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ 
     }
 }
 
+// The same two products for steps of few rows in bfloat16 (decoding), where the time goes into
+// reading the experts' weights once: a CTA of eight warps takes one row tile and 64 output
+// columns, holds up to ROWS_MAX of the tile's rows in shared memory (more: in turns), and every
+// warp walks its columns with 16-byte weight loads, the lanes across K, all rows at once; the
+// lanes' sums meet by butterfly.  A row's sums do not depend on the other rows.
+#define ROWS_MAX 8
+#define ROWS_COLS 64             // output columns per CTA, 8 per warp
+
+template <bool GATED, typename TO>
+__global__ void __launch_bounds__(256)
+moe_rows_kernel(const bf16* __restrict__ A, long long lda, const bf16* __restrict__ W, long long w_expert_stride,
+                TO* __restrict__ C, long long ldc, const int* __restrict__ perm, int top, const int3* __restrict__ tiles,
+                int max_tiles, int N, int K, int act, float limit, float alpha, float shift) {
+    extern __shared__ __align__(16) bf16 a_s[];            // [ROWS_MAX][K]
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    if ((int)blockIdx.y >= tiles[max_tiles].x) return;
+    const int3 tile = tiles[blockIdx.y];
+    const int e = tile.x, p0 = tile.y, rows = tile.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bf16* We = W + (size_t)e * w_expert_stride;
+    const int K8 = K / 8;
+    for (int r0 = 0; r0 < rows; r0 += ROWS_MAX) {
+        const int R = min(ROWS_MAX, rows - r0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < ROWS_MAX * K8; i += 256) {
+            const int r = i / K8, c = i - r * K8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < R) {
+                const int src = GATED ? perm[p0 + r0 + r] / top : p0 + r0 + r;
+                v = *reinterpret_cast<const uint4*>(A + (size_t)src * lda + c * 8);
+            }
+            *reinterpret_cast<uint4*>(a_s + (size_t)r * K + c * 8) = v;
+        }
+        __syncthreads();
+        for (int cc = 0; cc < ROWS_COLS / 8; ++cc) {
+            const int n = blockIdx.x * ROWS_COLS + warp * (ROWS_COLS / 8) + cc;
+            if (n >= N) break;
+            float acc[ROWS_MAX], acc2[GATED ? ROWS_MAX : 1];
+#pragma unroll
+            for (int r = 0; r < ROWS_MAX; ++r) {
+                acc[r] = 0.f;
+                if constexpr (GATED) acc2[r] = 0.f;
+            }
+            const bf16* w1 = We + (size_t)n * K;
+            const bf16* w2 = We + (size_t)(N + n) * K;
+#pragma unroll 2
+            for (int k = lane * 8; k < K; k += 256) {
+                const uint4 wv = *reinterpret_cast<const uint4*>(w1 + k);
+                uint4 wv2 = make_uint4(0, 0, 0, 0);
+                if constexpr (GATED) wv2 = *reinterpret_cast<const uint4*>(w2 + k);
+                const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+                const __nv_bfloat162* wp2 = reinterpret_cast<const __nv_bfloat162*>(&wv2);
+                float wf[8], wf2[8];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 t = __bfloat1622float2(wp[q]);
+                    wf[2 * q] = t.x; wf[2 * q + 1] = t.y;
+                    if constexpr (GATED) {
+                        const float2 u = __bfloat1622float2(wp2[q]);
+                        wf2[2 * q] = u.x; wf2[2 * q + 1] = u.y;
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < ROWS_MAX; ++r) {
+                    const uint4 av = *reinterpret_cast<const uint4*>(a_s + (size_t)r * K + k);
+                    const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float2 t = __bfloat1622float2(ap[q]);
+                        acc[r] = fmaf(t.y, wf[2 * q + 1], fmaf(t.x, wf[2 * q], acc[r]));
+                        if constexpr (GATED) acc2[r] = fmaf(t.y, wf2[2 * q + 1], fmaf(t.x, wf2[2 * q], acc2[r]));
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < ROWS_MAX; ++r) {
+                acc[r] = ap_warp_sum(acc[r]);
+                if constexpr (GATED) acc2[r] = ap_warp_sum(acc2[r]);
+            }
+            if (lane < R) {
+                float v = 0.f, v2 = 0.f;
+#pragma unroll
+                for (int r = 0; r < ROWS_MAX; ++r)
+                    if (r == lane) {
+                        v = acc[r];
+                        if constexpr (GATED) v2 = acc2[r];
+                    }
+                if constexpr (GATED) v = gated_activation(v, v2, act, limit, alpha, shift);
+                C[(size_t)(p0 + r0 + lane) * ldc + n] = ap_from_float<TO>(v);
+            }
+        }
+    }
+}
+
+// whether a step of `pairs` (row, choice) pairs in bfloat16 is one for the kernel above
+static bool moe_few_rows(int pairs, int E, int K, const void* a, const void* w) {
+    return pairs <= 16 * E && K % 8 == 0 && (size_t)ROWS_MAX * K * 2 <= 160 * 1024 &&
+           ((((uintptr_t)a) | ((uintptr_t)w)) & 15) == 0;
+}
+
 // a: [T, K]; w_gate_up: [E, 2 F, K]; y: [pairs, F] in the activation type
 AP_EXPORT int ap_moe_gate_up(const void* a, int a_dtype, const void* w, int w_dtype, void* y, int y_dtype,
                              const int* perm, int top, const int* tiles, int pairs, int E, int F, int K, int act,
@@ -331,6 +432,19 @@ AP_EXPORT int ap_moe_gate_up(const void* a, int a_dtype, const void* w, int w_dt
                                                      (const TA*)a, (long long)K, (const TW*)w, (long long)2 * F * K, \
                                                      (TO*)y, (long long)F, perm, top, (const int3*)tiles, max_tiles, F, K, \
                                                      act, limit, alpha, shift))
+    if (a_dtype == AP_BF16 && w_dtype == AP_BF16 && y_dtype == AP_BF16 && moe_few_rows(pairs, E, K, a, w)) {
+        const dim3 rgrid((unsigned)((F + ROWS_COLS - 1) / ROWS_COLS), (unsigned)max_tiles);
+        const size_t smem = (size_t)ROWS_MAX * K * sizeof(bf16);
+        auto kern = moe_rows_kernel<true, bf16>;
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            AP_REQUIRE(e == cudaSuccess, "moe_gate_up: cannot reserve %zu bytes of shared memory", smem);
+        }
+        AP_CHECK_PDL_LAUNCH("moe_gate_up", ap_launch_pdl(kern, rgrid, dim3(256), smem, stream, (const bf16*)a, (long long)K,
+                                                         (const bf16*)w, (long long)2 * F * K, (bf16*)y, (long long)F, perm,
+                                                         top, (const int3*)tiles, max_tiles, F, K, act, limit, alpha, shift));
+        return AP_OK;
+    }
     if (a_dtype == AP_F32 && w_dtype == AP_F32 && y_dtype == AP_F32) LAUNCH(float, float, float);
     else if (a_dtype == AP_BF16 && w_dtype == AP_BF16 && y_dtype == AP_BF16) LAUNCH(bf16, bf16, bf16);
     else if (a_dtype == AP_BF16 && w_dtype == AP_F32 && y_dtype == AP_BF16) LAUNCH(bf16, float, bf16);
@@ -352,6 +466,20 @@ AP_EXPORT int ap_moe_down(const void* y, int y_dtype, const void* w, int w_dtype
                                                   (const TA*)y, (long long)F, (const TW*)w, (long long)H * F, o,     \
                                                   (long long)H, (const int*)nullptr, 1, (const int3*)tiles, max_tiles, H, \
                                                   F, 0, 0.f, 0.f, 0.f))
+    if (y_dtype == AP_BF16 && w_dtype == AP_BF16 && moe_few_rows(pairs, E, F, y, w)) {
+        const dim3 rgrid((unsigned)((H + ROWS_COLS - 1) / ROWS_COLS), (unsigned)max_tiles);
+        const size_t smem = (size_t)ROWS_MAX * F * sizeof(bf16);
+        auto kern = moe_rows_kernel<false, float>;
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            AP_REQUIRE(e == cudaSuccess, "moe_down: cannot reserve %zu bytes of shared memory", smem);
+        }
+        AP_CHECK_PDL_LAUNCH("moe_down", ap_launch_pdl(kern, rgrid, dim3(256), smem, stream, (const bf16*)y, (long long)F,
+                                                      (const bf16*)w, (long long)H * F, o, (long long)H,
+                                                      (const int*)nullptr, 1, (const int3*)tiles, max_tiles, H, F, 0, 0.f,
+                                                      0.f, 0.f));
+        return AP_OK;
+    }
     if (y_dtype == AP_F32 && w_dtype == AP_F32) LAUNCH(float, float);
     else if (y_dtype == AP_BF16 && w_dtype == AP_BF16) LAUNCH(bf16, bf16);
     else if (y_dtype == AP_BF16 && w_dtype == AP_F32) LAUNCH(bf16, float);

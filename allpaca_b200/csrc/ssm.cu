@@ -104,7 +104,7 @@ AP_EXPORT int ap_causal_conv_silu(const float* in, long long ld_in, int col0, co
 // up to 32), whose partial sums of y meet by shuffles.  Tokens come SCAN_CHUNK at a time through
 // two shared-memory buffers filled by asynchronous copies: while one chunk is computed the next
 // one is on its way, so the chain over the tokens never waits for memory.
-#define NPT 16
+#define NPT 16                   // state entries per thread at most
 #define SCAN_CHUNK 16
 
 __device__ __forceinline__ void scan_copy4(float* dst, const float* src) {
@@ -116,6 +116,7 @@ __device__ __forceinline__ void scan_copy16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
 }
 
+template <int PER>               // state entries a thread holds: N <= PER * NP
 __global__ void __launch_bounds__(128)
 ssm_scan_kernel(const float* __restrict__ xbc, long long ld_xbc,           // [T, inner + 2 G N]: x | B | C
                 const float* __restrict__ dt_raw, long long ld_dt,         // [T, .]: column h is head h
@@ -142,9 +143,9 @@ ssm_scan_kernel(const float* __restrict__ xbc, long long ld_xbc,           // [T
     const int buf_floats = SCAN_CHUNK * (XS + 2 * NS) + 2 * SCAN_CHUNK;
     float* st = state + (size_t)state_slots[s] * state_stride + (size_t)h * N * vdim;
     const bool fresh = positions[a] == 0;
-    float S[NPT];
+    float S[PER];
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
+    for (int i = 0; i < PER; ++i) {
         const int nn = part + i * NP;
         S[i] = (!fresh && live && nn < N) ? st[(size_t)nn * vdim + v] : 0.f;
     }
@@ -213,12 +214,13 @@ ssm_scan_kernel(const float* __restrict__ xbc, long long ld_xbc,           // [T
             const float xv = live ? x_s[r * XS + vl] : 0.f;
             const float dx = dtv * xv;
             float acc = 0.f;
+            const float* br = b_s + r * NS + part;
+            const float* cr = c_s + r * NS + part;
 #pragma unroll
-            for (int i = 0; i < NPT; ++i) {
-                const int nn = part + i * NP;
-                if (nn < N) {
-                    S[i] = fmaf(decay, S[i], dx * b_s[r * NS + nn]);
-                    acc = fmaf(S[i], c_s[r * NS + nn], acc);
+            for (int i = 0; i < PER; ++i) {
+                if (part + i * NP < N) {
+                    S[i] = fmaf(decay, S[i], dx * br[i * NP]);
+                    acc = fmaf(S[i], cr[i * NP], acc);
                 }
             }
             for (int o = NP >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -228,7 +230,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, long long ld_xbc,           // [T
     }
     if (live) {
 #pragma unroll
-        for (int i = 0; i < NPT; ++i) {
+        for (int i = 0; i < PER; ++i) {
             const int nn = part + i * NP;
             if (nn < N) st[(size_t)nn * vdim + v] = S[i];
         }
@@ -246,8 +248,12 @@ AP_EXPORT int ap_ssm_scan(const float* xbc, long long ld_xbc, const float* dt_ra
     if (T == 0 || nseq == 0) return AP_OK;
     int NP = 1;
     while (NP * NPT < N) NP *= 2;
-    // at least four lanes to a column, so that a head of few columns still fills warps
+    // at least four lanes to a column, so that a head of few columns still fills warps; and more of them
+    // (shorter chains per thread, more warps) while the step's columns do not fill the GPU: the loop over
+    // a sequence's tokens is a chain of dependent instructions that only other warps can hide
     while (NP < 4 && NP < N) NP *= 2;
+    while (NP < 32 && NP < N && (long long)nseq * heads * vdim * NP / 32 < 148 * 16) NP *= 2;
+    const int per = (N + NP - 1) / NP;
     // value columns per CTA: CTAs of four warps, many of them, rather than few large ones: the loop over a
     // sequence's tokens is a chain, and what hides its latency is other chains on the same SM
     int cols = 128 / NP;
@@ -261,12 +267,13 @@ AP_EXPORT int ap_ssm_scan(const float* xbc, long long ld_xbc, const float* dt_ra
     const int vec = (cols % 4 == 0 && vdim % 4 == 0 && N % 4 == 0 && ld_xbc % 4 == 0 && ((uintptr_t)xbc & 15) == 0 &&
                      (heads * vdim) % 4 == 0) ? 1 : 0;
     const size_t smem = 2 * ((size_t)SCAN_CHUNK * ((cols + 3) / 4 * 4 + 2 * ((N + 3) / 4 * 4)) + 2 * SCAN_CHUNK) * sizeof(float);
+    auto kern = per <= 4 ? ssm_scan_kernel<4> : ssm_scan_kernel<NPT>;
     if (smem > 48 * 1024) {
         AP_REQUIRE(smem <= 200 * 1024, "ssm_scan: a state of %d entries does not fit the staging buffers", N);
-        cudaError_t e = cudaFuncSetAttribute(ssm_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         AP_REQUIRE(e == cudaSuccess, "ssm_scan: cannot reserve %zu bytes of shared memory", smem);
     }
-    AP_CHECK_PDL_LAUNCH("ssm_scan", ap_launch_pdl(ssm_scan_kernel, grid, dim3(threads), smem, stream, xbc, ld_xbc, dt_raw,
+    AP_CHECK_PDL_LAUNCH("ssm_scan", ap_launch_pdl(kern, grid, dim3(threads), smem, stream, xbc, ld_xbc, dt_raw,
                                                   ld_dt, dt_bias, a_log, d_skip, state, state_stride, seq_start,
                                                   positions, state_slots, y, heads, groups, N, vdim, NP, cols, vec));
     return AP_OK;

@@ -62,8 +62,8 @@ class DistanceBiasedAttention(Mixer):
         w = {"q": WeightSpec((self.q_size, self.hidden)), "k": WeightSpec((self.k_size, self.hidden)),
              "v": WeightSpec((self.v_size, self.hidden)), "o": WeightSpec((self.hidden, self.nh * self.vd))}
         if self.distance_bias:
-            w["r1"] = WeightSpec((self.nh,), "bias")
-            w["r2"] = WeightSpec((self.nh,), "bias")
+            w["r1"] = WeightSpec((self.nh,), "positive")
+            w["r2"] = WeightSpec((self.nh,), "positive")
         return w
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:

@@ -120,7 +120,7 @@ class WeightSpec:
     """One tensor a part needs: its shape and what it is (decides type and random init)."""
 
     shape: Tuple[int, ...]
-    role: str = "linear"      # "linear" | "embedding" | "norm" | "bias" | "table"
+    role: str = "linear"      # "linear" | "embedding" | "norm" | "bias" | "positive" | "table"
     optional: bool = False
 
 

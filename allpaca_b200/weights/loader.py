@@ -121,6 +121,9 @@ def random_tensor(name: str, spec: WeightSpec, seed: int, dtype: torch.dtype,
             t.normal_(0.0, norm_std, generator=gen).add_(1.0)
         else:
             t.fill_(1.0)
+    elif spec.role == "positive":
+        # numbers a model only makes sense with when they are positive (a factor inside a logarithm)
+        t.uniform_(0.05, 1.0, generator=gen)
     else:
         t.normal_(0.0, std, generator=gen)
     return t.to(dtype)
