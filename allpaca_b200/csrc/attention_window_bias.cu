@@ -533,8 +533,9 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
             const TA* kr = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * (D + VD);
             if (sizeof(TA) == 2 && D % 8 == 0 && (D + VD) % 8 == 0 && (page_stride % 8) == 0 &&
                 ((uintptr_t)cache & 15) == 0) {
-                // eight 16-bit elements of the key's row per load
-#pragma unroll 4
+                // eight 16-bit elements of the key's row per load; unrolled far, so that a lane's loads of a
+                // whole row are in flight together
+#pragma unroll 16
                 for (int d = 0; d < D; d += 8) {
                     const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(kr) + d);
                     const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -573,7 +574,7 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
             const TA* vr = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * (D + VD) + D;
             TA* dst = v_s + lane * VDP;
             if (sizeof(TA) == 2 && D % 8 == 0 && VD % 8 == 0 && (page_stride % 8) == 0 && ((uintptr_t)cache & 15) == 0) {
-#pragma unroll 4
+#pragma unroll 16
                 for (int d = 0; d < VD; d += 8)
                     *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + d) =
                         *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(vr) + d);

@@ -363,7 +363,7 @@ moe_rows_kernel(const bf16* __restrict__ A, long long lda, const bf16* __restric
             }
             const bf16* w1 = We + (size_t)n * K;
             const bf16* w2 = We + (size_t)(N + n) * K;
-#pragma unroll 2
+#pragma unroll 4
             for (int k = lane * 8; k < K; k += 256) {
                 const uint4 wv = *reinterpret_cast<const uint4*>(w1 + k);
                 uint4 wv2 = make_uint4(0, 0, 0, 0);
