@@ -60,7 +60,11 @@ def paged(kv, P, order):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("H,G,D,E,P,window", [(4, 2, 24, 40, 8, 21), (2, 2, 64, 64, 16, 72), (3, 1, 16, 80, 16, None),
-                                              (8, 8, 128, 32, 32, 300), (1, 1, 8, 8, 8, 1)])
+                                              (8, 8, 128, 32, 32, 300), (1, 1, 8, 8, 8, 1),
+                                              # sizes that are no multiple of 8 (no 16-byte runs), an odd one, more
+                                              # than 8 query heads to a key/value head, and heads over 128
+                                              (2, 1, 20, 12, 8, 11), (2, 2, 33, 7, 16, 40), (12, 1, 16, 16, 8, 64),
+                                              (2, 1, 160, 136, 16, 100)])
 def test_attention_with_a_key_that_stands_out(dtype, tol, H, G, D, E, P, window):
     """Two sequences in one launch: a portion of 37 rows behind 300 cached tokens and a single
     decoded row at position 333 of another.  In each, one key is made to dominate for chosen

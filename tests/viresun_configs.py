@@ -49,4 +49,17 @@ VIRESUN_B = {
         {"type": "attention", "mixer": attention(2, 2, 32, 64, 0.2, q_temp=(0.25, 7)), "mlp": dense(64)},
     ],
 }
-CONFIGS = {"A": VIRESUN_A, "B": VIRESUN_B}
+# a width that is no multiple of 8 (no tensor-core product takes it), head sizes 20 and 12, a window of one (a row
+# sees itself alone) beside none, a convolution of one tap (no inputs carried), every Mamba head its own group and
+# norm part, an attention layer that borrows tensors, 3 experts of which 2 are chosen, an odd vocabulary
+VIRESUN_C = {
+    "architecture": "Viresun", "vocab": 97, "width": 44, "norm": {"eps": 3e-6},
+    "layers": [
+        {"type": "attention", "mixer": attention(3, 3, 20, 12, 0.4, window=1, q_temp=(1.0, 3)), "mlp": moe(16, 3, 2, 0.8)},
+        {"type": "mamba2", "mixer": mamba(2, 10, 6, 2, 1, 2), "mlp": None},
+        {"type": "attention", "mixer": attention(4, 2, 12, 20, 0.35), "mlp": dense(52)},
+        {"type": "attention", "mixer": attention(3, 3, 20, 12, 0.4, window=1, q_temp=(1.0, 3)), "mlp": moe(16, 3, 2, 0.8),
+         "weights_of": 0},
+    ],
+}
+CONFIGS = {"A": VIRESUN_A, "B": VIRESUN_B, "C": VIRESUN_C}
