@@ -471,16 +471,18 @@ static int launch_awb_mma(const void* q, void* out, const void* cache, const int
 // ---------------------------------------------------------------------------------------
 // Sequences that bring one row (decoding).  One CTA per (sequence, key/value head): the query
 // heads that share the key/value head are served together, so every key and value is read
-// once for all of them.  The four warps take the key tiles in turn (tile i goes to warp
-// i mod 4), each with an online softmax of its own; a lane reads its key's row straight from
+// once for all of them.  The eight warps take the key tiles in turn (tile i goes to warp
+// i mod 8), each with an online softmax of its own; a lane reads its key's row straight from
 // the page, values come row by row with the lanes across the columns; at the end the warps'
 // partial results meet in shared memory and are merged in warp order.  Sequences with
 // another number of rows are left to the kernel above (`skip_single` there).
 // ---------------------------------------------------------------------------------------
 #define DEC_REP_MAX 8             // query heads per CTA at most (more: the grid's z walks them)
+#define DEC_WARPS 8               // the kernel is a chain of dependent steps per key tile: eight warps share the tiles
+#define DEC_THREADS (DEC_WARPS * 32)
 
 template <typename TA, int DEC_REP>   // DEC_REP: query heads per CTA this kernel is built for (1, 2, 4, 8)
-__global__ void __launch_bounds__(AWB_THREADS)
+__global__ void __launch_bounds__(DEC_THREADS)
 attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ out, const TA* __restrict__ cache,
                                     const int* __restrict__ block_table, int max_blocks,
                                     const int* __restrict__ seq_start, const int* __restrict__ positions, int nh,
@@ -499,12 +501,14 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int NC = MAX_HEAD / 32;
     float* q_s = smem;                                   // [DEC_REP][D]
-    float* p_s = q_s + DEC_REP * D;                      // [AWB_WARPS][DEC_REP][KT]
-    float* part = p_s + AWB_WARPS * DEC_REP * KT;        // [AWB_WARPS][DEC_REP][VD + 2]
-    const int VDP = (VD + 7) / 8 * 8;                    // a value row in shared memory, padded to 16-byte runs
-    TA* v_s = reinterpret_cast<TA*>(smem + ((DEC_REP * D + AWB_WARPS * DEC_REP * KT + AWB_WARPS * DEC_REP * (VD + 2) + 3) / 4) * 4) +
+    float* p_s = q_s + DEC_REP * D;                      // [DEC_WARPS][DEC_REP][KT]
+    float* part = p_s + DEC_WARPS * DEC_REP * KT;        // [DEC_WARPS][DEC_REP][VD + 2]
+    // a value row in shared memory: whole 16-byte runs, and 16 bytes more, so that the lanes' rows start in
+    // different banks (rows of exactly 256 bytes would put all 32 lanes' stores on the same four banks)
+    const int VDP = (VD + 7) / 8 * 8 + 8;
+    TA* v_s = reinterpret_cast<TA*>(smem + ((DEC_REP * D + DEC_WARPS * DEC_REP * KT + DEC_WARPS * DEC_REP * (VD + 2) + 3) / 4) * 4) +
               (size_t)warp * KT * VDP;                       // [KT][VDP] per warp, on a 16-byte boundary
-    for (int i = threadIdx.x; i < rep * D; i += AWB_THREADS)
+    for (int i = threadIdx.x; i < rep * D; i += DEC_THREADS)
         q_s[i] = ap_to_float(q[((size_t)row * nh + h0) * D + i]);
     __syncthreads();
     const int qpos = positions[row];
@@ -523,7 +527,7 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
     const int nc = (VD + 31) / 32;
     float* pw = p_s + warp * DEC_REP * KT;
     const int first_tile = klo / KT;
-    for (int tile = first_tile + warp; tile * KT <= qpos; tile += AWB_WARPS) {
+    for (int tile = first_tile + warp; tile * KT <= qpos; tile += DEC_WARPS) {
         const int kp = tile * KT + lane;
         const bool seen = kp >= klo && kp <= qpos;
         float s[DEC_REP];
@@ -618,12 +622,12 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
         }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < rep * VD; e += AWB_THREADS) {
+    for (int e = threadIdx.x; e < rep * VD; e += DEC_THREADS) {
         const int i = e / VD, d = e - i * VD;
         float mm = -FLT_MAX;
-        for (int w = 0; w < AWB_WARPS; ++w) mm = fmaxf(mm, part[(w * DEC_REP + i) * PW + VD]);
+        for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, part[(w * DEC_REP + i) * PW + VD]);
         float num = 0.f, den = 0.f;
-        for (int w = 0; w < AWB_WARPS; ++w) {
+        for (int w = 0; w < DEC_WARPS; ++w) {
             const float* src = part + (w * DEC_REP + i) * PW;
             const float f = expf(src[VD] - mm);          // 0 for a warp that saw no key (its maximum is -FLT_MAX)
             num = fmaf(src[d], f, num);
@@ -655,9 +659,9 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         while (rep_chunk < DEC_REP_MAX && rep_chunk < rep) rep_chunk *= 2;
         while (rep_chunk > 1 && (long long)nseq * nkv * ((rep + rep_chunk - 1) / rep_chunk) < 2 * 148) rep_chunk /= 2;
         const dim3 dgrid((unsigned)nseq, (unsigned)nkv, (unsigned)((rep + rep_chunk - 1) / rep_chunk));
-        const size_t dsmem = ((size_t)rep_chunk * D + (size_t)AWB_WARPS * rep_chunk * KT +
-                              (size_t)AWB_WARPS * rep_chunk * (VD + 2)) * sizeof(float) +
-                             (size_t)AWB_WARPS * KT * ((VD + 7) / 8 * 8) * (dtype == AP_F32 ? 4 : 2) + 16;
+        const size_t dsmem = ((size_t)rep_chunk * D + (size_t)DEC_WARPS * rep_chunk * KT +
+                              (size_t)DEC_WARPS * rep_chunk * (VD + 2)) * sizeof(float) +
+                             (size_t)DEC_WARPS * KT * ((VD + 7) / 8 * 8 + 8) * (dtype == AP_F32 ? 4 : 2) + 16;
         AP_REQUIRE(nkv <= 65535, "attention_window_bias: %d key/value heads exceed the grid", nkv);
 #define LAUNCH_DEC(TA)                                                                                               \
     do {                                                                                                             \
@@ -670,7 +674,7 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
             AP_REQUIRE(e == cudaSuccess, "attention_window_bias: cannot reserve %zu bytes of shared memory", dsmem); \
         }                                                                                                            \
         AP_CHECK_PDL_LAUNCH("attention_window_bias_decode",                                                          \
-                            ap_launch_pdl(kern, dgrid, dim3(AWB_THREADS), dsmem, stream, (const TA*)q, (TA*)out,     \
+                            ap_launch_pdl(kern, dgrid, dim3(DEC_THREADS), dsmem, stream, (const TA*)q, (TA*)out,     \
                                           (const TA*)cache, block_table, max_blocks, seq_start, positions, nh, nkv,  \
                                           D, VD, P, (size_t)page_stride, scale, window, r1, r2));                    \
     } while (0)
