@@ -81,3 +81,23 @@ def test_plain_prefix_property():
     whole = plain_viresun.forward(config, w, tokens)
     part = plain_viresun.forward(config, w, tokens[:27])
     assert float((whole[:27] - part).abs().max()) < 1e-9
+
+
+def test_random_model_folder_from_the_command_line(tmp_path):
+    """``allpaca init-random --config`` writes a Viresun folder the engine's reader accepts: every tensor
+    the description names, the numbers inside the bias's logarithm positive, the norms' weights one
+    number each."""
+    import json
+    from allpaca_b200 import cli
+    from allpaca_b200.models import load_config
+    from allpaca_b200.weights.safetensors_io import Checkpoint
+    src = tmp_path / "config.json"
+    src.write_text(json.dumps(VIRESUN_A))
+    assert cli.main(["init-random", "--config", str(src), "--seed", "3", "--out", str(tmp_path / "m"),
+                     "--dtype", "bfloat16"]) == 0
+    arch, cfg = load_config(str(tmp_path / "m"))
+    assert arch.name == "Viresun" and cfg.torch_dtype == "bfloat16" and len(cfg.layers) == 5
+    ckpt = Checkpoint(str(tmp_path / "m"))
+    assert set(ckpt.names()) == set(plain_viresun.tensor_shapes(VIRESUN_A))
+    assert float(ckpt.tensor("l0.mix.r2").float().min()) > 0 and float(ckpt.tensor("l3.mix.r1").float().min()) > 0
+    assert tuple(ckpt.tensor("l1.norm2").shape) == ()
