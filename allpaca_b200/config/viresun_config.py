@@ -44,12 +44,15 @@ class AttentionMixerConfig:
 
     @classmethod
     def from_dict(cls, d: Mapping[str, Any], where: str) -> "AttentionMixerConfig":
-        heads, kv = _int(d, "heads", where), _int(d, "kv_heads", where)
+        heads = _int(d, "heads", where)
+        kv = _int(d, "kv_heads", where) if d.get("kv_heads") is not None else heads     # left out: one per query head
         if heads % kv:
             raise ConfigError(f"{where}: {heads} heads are not a multiple of {kv} kv_heads")
         mask = d.get("mask") or None
         temp = d.get("q_temp") or None
-        return cls(heads=heads, kv_heads=kv, dim=_int(d, "dim", where), vdim=_int(d, "vdim", where),
+        dim = _int(d, "dim", where)
+        return cls(heads=heads, kv_heads=kv, dim=dim,
+                   vdim=_int(d, "vdim", where) if d.get("vdim") is not None else dim,      # left out: the key's size
                    scale=_float(d, "scale", where),
                    window=_int(mask, "size", where + ".mask") if mask else None,
                    q_temp=(_float(temp, "coef", where + ".q_temp"), _int(temp, "every", where + ".q_temp"))
@@ -68,8 +71,9 @@ class Mamba2MixerConfig:
     @classmethod
     def from_dict(cls, d: Mapping[str, Any], where: str) -> "Mamba2MixerConfig":
         out = cls(heads=_int(d, "heads", where), vdim=_int(d, "vdim", where), state=_int(d, "state", where),
-                  groups=_int(d, "groups", where), conv=_int(d, "conv", where),
-                  norm_groups=_int(d, "norm_groups", where))
+                  groups=_int(d, "groups", where) if d.get("groups") is not None else 1,
+                  conv=_int(d, "conv", where),
+                  norm_groups=_int(d, "norm_groups", where) if d.get("norm_groups") is not None else 1)
         if out.heads % out.groups:
             raise ConfigError(f"{where}: {out.heads} heads are not a multiple of {out.groups} groups")
         if (out.heads * out.vdim) % out.norm_groups:

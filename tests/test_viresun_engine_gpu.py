@@ -13,7 +13,7 @@ import torch
 
 import helpers
 import plain_viresun
-from viresun_configs import CONFIGS
+from viresun_configs import CONFIGS, VIRESUN_ONLY_ATTENTION, VIRESUN_ONLY_MAMBA
 
 pytestmark = pytest.mark.gpu
 
@@ -190,6 +190,45 @@ def test_batch_and_cut_do_not_change_32_bit_rows(tmp_path):
     first = runner.step([BatchEntry("b", b[:20], []), BatchEntry("a", a[:41], list(range(41)))]).clone()
     second = runner.step([BatchEntry("a", a[41:], list(range(29))), BatchEntry("b", b[20:], [])]).clone()
     assert torch.equal(torch.cat([first, second]), alone)
+
+
+@pytest.mark.parametrize("config", [VIRESUN_ONLY_MAMBA, VIRESUN_ONLY_ATTENTION], ids=["only-mamba", "only-attention"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_models_of_one_kind_of_mixer(tmp_path, config, dtype):
+    """A model without any attention has no page group, one without a recurrent mixer no state: both run,
+    two requests side by side, portions and single rows."""
+    from allpaca_b200.engine.batch import BatchEntry
+    config = config if dtype == "float32" else every_expert_chosen(config)
+    weights = write_folder(tmp_path, config, seed=2, dtype=dtype)
+    a, b = helpers.random_tokens(40, config["vocab"], 5), helpers.random_tokens(27, config["vocab"], 6)
+    plain = {"a": plain_viresun.forward(config, weights, a), "b": plain_viresun.forward(config, weights, b)}
+    runner = make_runner(tmp_path, dtype, 128, max_seqs=2)
+    only_mamba = all(layer["type"] == "mamba2" for layer in config["layers"])
+    assert len(runner.cache_plan) == (0 if only_mamba else 2)          # two attention layers of different shapes
+    assert [s is not None for s in runner.states] == [only_mamba, only_mamba]
+    tally = Tally()
+    logits = runner.step([BatchEntry("a", a[:11], list(range(11))), BatchEntry("b", b[:1], [0])])
+    check(logits[:11], plain["a"][:11], TOL[dtype], "a head", tally)
+    check(logits[11:], plain["b"][:1], TOL[dtype], "b head", tally)
+    at = {"a": 11, "b": 1}
+    toks = {"a": a, "b": b}
+    while at["a"] < 40 or at["b"] < 27:
+        entries, rows = [], []
+        for r in ("b", "a"):
+            if at[r] < len(toks[r]):
+                n = 1 if at[r] % 3 else min(4, len(toks[r]) - at[r])
+                entries.append(BatchEntry(r, toks[r][at[r]:at[r] + n], list(range(n))))
+                rows.append((r, at[r], n))
+                at[r] += n
+        logits = runner.step(entries)
+        k = 0
+        for r, first, n in rows:
+            check(logits[k:k + n], plain[r][first:first + n], TOL[dtype], (r, first, n), tally)
+            k += n
+    tally.finish(dtype)
+    runner.finish("a")
+    runner.finish("b")
+    runner.cache.check()
 
 
 def test_trace_runner_as_a_user_starts_it(tmp_path):

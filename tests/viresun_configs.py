@@ -62,4 +62,15 @@ VIRESUN_C = {
          "weights_of": 0},
     ],
 }
+# no attention at all (no page group, states only), and no recurrent mixer at all (pages only)
+VIRESUN_ONLY_MAMBA = {
+    "architecture": "Viresun", "vocab": 64, "width": 32, "norm": {"eps": 1e-5},
+    "layers": [{"type": "mamba2", "mixer": mamba(2, 8, 12, 1, 3, 2), "mlp": dense(40)},
+               {"type": "mamba2", "mixer": mamba(4, 4, 5, 2, 2, 1), "mlp": moe(16, 4, 2, 1.0)}],
+}
+VIRESUN_ONLY_ATTENTION = {
+    "architecture": "Viresun", "vocab": 64, "width": 32, "norm": {"eps": 1e-5},
+    "layers": [{"type": "attention", "mixer": attention(2, 1, 16, 8, 0.25, window=9), "mlp": None},
+               {"type": "attention", "mixer": attention(4, 4, 8, 8, 0.3, q_temp=(0.5, 4)), "mlp": dense(48)}],
+}
 CONFIGS = {"A": VIRESUN_A, "B": VIRESUN_B, "C": VIRESUN_C}
