@@ -268,3 +268,19 @@ def test_greedy_generation_through_the_entry_point(tmp_path, dtype):
             for i, t in enumerate(o.token_ids):
                 row = logits[len(p) + i - 1]
                 assert float(row.max() - row[t]) <= 2 * TOL[dtype] * float(logits.abs().max()), (i, t)
+
+
+def test_preempted_requests_start_their_state_again(tmp_path):
+    """A pool too small for three requests: the scheduler preempts one (pages and state slot given back)
+    and computes it again from position 0 later; its recurrent state starts from zero there, and the
+    tokens equal the plain implementation's."""
+    from allpaca_b200 import LLM, SamplingParams
+    config = CONFIGS["B"]
+    weights = write_folder(tmp_path, config, seed=15, dtype="float32")
+    prompts = [helpers.random_tokens(n, config["vocab"], 90 + n) for n in (30, 28, 26)]
+    llm = LLM(model=str(tmp_path), dtype="float32", page_size=16, max_cache_tokens=96, max_num_seqs=3,
+              max_num_batched_tokens=64, prefill_chunk=32)
+    outs = llm.generate(prompts, SamplingParams.greedy_params(max_tokens=10))
+    assert sum(o.num_preemptions for o in outs) > 0, "the pool was meant to run out"
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain_viresun.greedy(config, weights, p, 10), (p[:3], o.token_ids)
