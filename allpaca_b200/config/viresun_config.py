@@ -4,7 +4,8 @@ feed-forward (dense, routed, or none), possibly borrowing another layer's weight
 
 config.json gives every size and constant: ``vocab``, ``width``, ``norm.eps`` and ``layers``,
 a list of ``{"type", "mixer": {...}, "mlp": {...} | null, "weights_of": j}`` (the last optional:
-the layer runs layer ``j``'s tensors with a cache or state of its own).  Nothing is defaulted
+such a layer owns no tensors and computes with those of layer ``j``; what it caches per request
+stays separate).  Nothing is defaulted
 that the configuration must say; what a mechanism may leave out (a window, a query
 temperature) is None.
 """

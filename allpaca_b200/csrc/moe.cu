@@ -1,7 +1,7 @@
 // A routed feed-forward (mixture of experts) and the gated activations of feed-forwards:
 //
 //   moe_route      per row: the `top` experts with the largest router logits (ties: the lower
-//                  index), weights = softmax over the chosen logits; all 32-bit
+//                  index), shares = exp(z_e) / sum over the selected exp(z_s); all 32-bit
 //   moe_sort       (row, choice) pairs grouped by expert: a permutation, every pair's place in
 //                  it, and a list of row tiles (expert, first place, rows) for the products
 //   moe_gate_up    for every tile: y = act(A W_gate[e]^T, A W_up[e]^T), rows gathered by the permutation

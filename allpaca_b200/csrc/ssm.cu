@@ -1,7 +1,7 @@
 // A selective state-space mixer in its recurrent form (state-space duality, one scalar decay
 // per head), with the state a request carries from step to step:
 //
-//   causal_conv_silu   u_t[c] = silu(b[c] + sum_j w[c][j] * in_{t-(taps-1)+j}[c])     (zeros before position 0)
+//   causal_conv_silu   u_t[c] = silu(b[c] + sum_j w[c][j] * in_{t-(taps-1)+j}[c])     (in_t = 0 for t < 0)
 //   conv_state_update  the last taps-1 inputs of every sequence, for its next step
 //   ssm_scan           dt = softplus(raw + dt_bias[h]);  S_t = exp(-exp(A_log[h]) dt) S_{t-1} + dt B_t x_t^T;
 //                      y_t = S_t^T C_t + D[h] x_t                                        (S: [N, vdim] per head)
@@ -279,7 +279,7 @@ AP_EXPORT int ap_ssm_scan(const float* xbc, long long ld_xbc, const float* dt_ra
     return AP_OK;
 }
 
-// ---- gate, then RMS norm in equal parts of the row --------------------------------------
+// ---- gate, then RMS norm per slice of the row -------------------------------------------
 // y: [T, inner] 32-bit; z: [T, ld_z] 32-bit gate (column 0 of the view); one warp per (row, part).
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(128)

@@ -5,8 +5,8 @@ norms have one number as their weight; per layer a mixer (attention without rota
 RMS norm of queries and keys, a query temperature that grows with the logarithm of the position,
 a logarithmic distance bias per head, a sliding window; or a Mamba-2 state-space mixer) and a
 feed-forward (ReLU-gated dense, routed experts with a clamped sigmoid gate, or none); final norm
-and head.  A layer may run another layer's tensors with a cache or state of its own: it is then a
-second entry of the order that names the same layer.
+and head.  A layer that owns no tensors and computes with another layer's is a second entry of the
+order naming that layer; the engine gives every entry of the order separate pages and state.
 
 Tensor names: ``embed``, ``embed.norm``, ``l<i>.norm1``, ``l<i>.norm2``, ``l<i>.mix.*``,
 ``l<i>.mlp.*``, ``final.norm``, ``head``.

@@ -55,7 +55,7 @@ def qk_norm_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[
                   num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, eps: float,
                   normalise: bool = True, temp_coef: float = 0.0, temp_every: int = 0) -> None:
     """Prepare the operands of :func:`attention_window_bias` from the stacked projection
-    ``qkv [T, nh*D + nkv*D + nkv*VD]``: every query and key head divided by its root mean square
+    ``qkv [T, nh*D + nkv*D + nkv*VD]``: every query and key head rescaled to unit mean square
     (``normalise``), queries multiplied by ``1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)``
     (``temp_every`` 0: no temperature) into ``q_out [T, nh*D]``, keys and values into the pages
     ``cache_layer [pages, nkv, P, D + VD]`` (None: not stored)."""
@@ -123,7 +123,7 @@ def causal_conv_silu(inp: torch.Tensor, col0: int, weight: torch.Tensor, bias: O
                      state: Optional[torch.Tensor], token_seq: torch.Tensor, seq_start: torch.Tensor,
                      positions: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor, num_seqs: int) -> None:
     """``out[t, c] = silu(bias[c] + sum_j weight[c, j] * in[t - (taps-1) + j, col0 + c])`` per
-    sequence, zeros before position 0; ``state [slots, taps-1, C]`` (32-bit, may be a strided
+    sequence, inputs of negative positions being zero; ``state [slots, taps-1, C]`` (32-bit, may be a strided
     view of the slots' rows) supplies the inputs from before the step and is brought up to date."""
     _check(inp, "in", torch.float32, 2)
     _check(weight, "weight", torch.float32, 2)
@@ -185,8 +185,8 @@ def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: Optional[torch.Te
 
 def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: Optional[torch.Tensor], eps: float,
                         out: torch.Tensor, parts: int) -> None:
-    """``out = rmsnorm(y * silu(z)) * weight`` with the root mean square taken over each of
-    ``parts`` equal parts of a row; ``y [T, inner]`` 32-bit, ``z`` a 32-bit (strided) view of the
+    """``out = rmsnorm(y * silu(z)) * weight`` where a row is cut into ``parts`` slices of equal
+    length and every slice is normalised on its own; ``y [T, inner]`` 32-bit, ``z`` a 32-bit (strided) view of the
     same shape."""
     _check(y, "y", torch.float32, 2)
     _check(out, "out", dims=2)

@@ -1,12 +1,13 @@
 """Grouped-query attention without a rotation, whose positions enter through the scores:
 
-* queries and keys are divided by their root mean square over the head (an RMS norm without a
-  weight, ``qk_norm_eps``; None: not normalised);
+* every query head and every key head is rescaled to unit mean square, ``v / sqrt(mean(v^2) + eps)``
+  with ``eps = qk_norm_eps`` and no learned gain (None: left as projected);
 * the query at position ``p`` is multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)``
   (``q_temp = {"coef", "every"}``; None: no temperature);
-* ``score(i, j) = (q_i . k_j) * scale - r1[h] * ln(1 + r2[h] * (i - j))`` with one pair of
-  numbers per query head (``distance_bias``; False: no bias and no tensors ``r1``, ``r2``);
-* position ``i`` sees ``j`` with ``0 <= i - j < window`` (None: every earlier key);
+* ``score(i, j) = (q_i . k_j) * scale - r1[h] * ln(1 + r2[h] * (i - j))``: a penalty that grows with
+  the logarithm of the distance, two numbers per query head (``distance_bias``; False: neither the
+  penalty nor the tensors ``r1``, ``r2``);
+* the keys of a query at position ``i`` are those at ``i - window + 1 .. i`` (None: ``0 .. i``);
 * keys and values may differ in size (``head_dim``, ``value_dim``).
 
 A token keeps its key and value side by side in pages ``[kv_heads, page, head_dim + value_dim]``;

@@ -320,8 +320,8 @@ class ModelSpec:
     max_position_embeddings: int = 2048
     # Ends of the stack that some decoders alter; all default to "as it is".
     embedding_scale: Optional[float] = None      # the gathered embedding row is multiplied by it
-    # a sinusoidal position vector added to the embedding row: entry 2i is sin(p * base^(-2i/width)),
-    # entry 2i+1 the cosine of the same angle (None: no position vector)
+    # sinusoidal position vector added to the embedding row: with angle a_i = p * base^(-2i/width), column 2i
+    # holds sin(a_i) and column 2i+1 holds cos(a_i) (None: no position vector)
     embedding_sinusoid_base: Optional[float] = None
     embedding_norm: Optional[PartSpec] = None    # a norm applied to the embedding row (after the position vector)
     embedding_norm_prefix: str = "model.embed_norm."

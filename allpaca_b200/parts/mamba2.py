@@ -2,14 +2,15 @@
 in its recurrent form.
 
 With ``inner = heads * value_dim``, ``N = state_size`` and ``G = groups``, the input projection
-of a row is laid out ``[z: inner | x: inner | B: G*N | C: G*N | dt: heads]``.  ``x``, ``B`` and
-``C`` together pass a causal convolution per channel over ``conv_taps`` tokens (weight
-``[channels, taps]``, the last column the current token's; bias; zeros before the start) and
-SiLU.  ``dt = softplus(dt + dt_bias)``; per head ``h`` (group ``h // (heads / G)``):
-``S_t = exp(-exp(A_log[h]) dt) S_{t-1} + dt B_t x_t^T`` (``S`` is ``N x value_dim``) and
-``y_t = S_t^T C_t + D[h] x_t``.  ``y`` is multiplied by ``silu(z)``, RMS-normed in
-``norm_groups`` equal parts of the row (each by its own root mean square) times the weight
-``norm``, then projected out.
+of a row splits into ``z`` (inner), ``x`` (inner), ``B`` (G*N), ``C`` (G*N) and ``dt`` (heads), in
+this order.  The ``x | B | C`` columns go through a depthwise convolution along the sequence,
+``u_t[c] = b[c] + sum_j w[c, j] * in_{t - (taps-1) + j}[c]`` with inputs of negative positions
+taken as zero (so ``w[c, taps-1]`` weighs the row itself), followed by SiLU.  The step size is
+``dt = softplus(dt + dt_bias)``; head ``h`` reads ``B`` and ``C`` of group ``h // (heads / G)`` and
+keeps a state ``S`` of ``N x value_dim``: ``S_t = exp(-exp(A_log[h]) dt) S_{t-1} + dt B_t x_t^T``,
+``y_t = S_t^T C_t + D[h] x_t``.  The gated output ``y * silu(z)`` is cut into ``norm_groups``
+slices of equal length, each slice rescaled to unit mean square on its own, multiplied by the
+weight ``norm`` and projected out.
 
 What a request carries between steps is a state of fixed size: ``S`` of every head and the last
 ``conv_taps - 1`` inputs of the convolution, both 32-bit, in the request's state slot.  A portion

@@ -1,8 +1,9 @@
 """A routed feed-forward: ``experts`` small gated feed-forward layers, of which every row uses
 the ``top`` whose router logits are largest.
 
-Router logits ``z = W_router h + b`` are 32-bit; the chosen experts' weights are the softmax
-over the chosen logits only; the output is the weighted sum of the chosen experts' outputs.
+Router logits ``z = W_router h + b`` are 32-bit.  With ``S`` the set of the ``top`` largest,
+expert ``e`` in ``S`` gets the share ``exp(z_e) / sum_{s in S} exp(z_s)`` and the layer returns
+``sum_{e in S} share_e * expert_e(h)``.
 An expert is ``W_down act(W_gate h, W_up h)`` without biases, ``act`` one of the gated
 activations of ``ops.gated_act`` (``clamped_sigmoid``: ``g' = min(g, limit)``,
 ``u' = clamp(u, -limit, limit)``, ``g' sigmoid(alpha g') (u' + shift)``).

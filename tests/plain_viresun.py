@@ -80,7 +80,7 @@ def silu(z):
 
 
 def causal_conv(u: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
-    """u [T, C]; weight [C, taps], the last column multiplies the current token; zeros before 0."""
+    """u [T, C]; weight [C, taps]: tap j weighs the row taps-1-j tokens back; rows of negative index are zero."""
     T, C = u.shape
     taps = weight.shape[1]
     out = bias.expand(T, C).clone()
