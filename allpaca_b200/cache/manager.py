@@ -68,7 +68,7 @@ def host_library() -> ctypes.CDLL:
             getattr(lib, name).restype = c_int
         lib.apc_cache_num_tokens.argtypes = [c_void_p, c_int64]
         lib.apc_cache_num_tokens.restype = c_int64
-        lib.apc_cache_create.argtypes = [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), c_int]
+        lib.apc_cache_create.argtypes = [c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int), c_int]
         lib.apc_cache_create.restype = c_void_p
         lib.apc_cache_destroy.argtypes = [c_void_p]
         lib.apc_cache_destroy.restype = None
@@ -167,11 +167,14 @@ class PagePool:
 
 @dataclass(frozen=True)
 class GroupLayout:
-    """One cache group: its page size, pool size and window (None: keep everything)."""
+    """One cache group: its page size, pool size and window (None: keep everything).  With a
+    window, ``keep_first`` tokens at the start of every request stay readable for good: their pages
+    are never given back while the request runs."""
 
     page_size: int
     num_pages: int
     window: Optional[int] = None
+    keep_first: int = 0
 
 
 class CacheManager:
@@ -187,6 +190,8 @@ class CacheManager:
                 raise CacheError(f"a page pool needs at least one page, got {g.num_pages}")
             if g.window is not None and g.window <= 0:
                 raise CacheError("a window must be positive")
+            if g.keep_first < 0:
+                raise CacheError("keep_first must not be negative")
         self.groups = list(groups)
         self.max_seqs = int(max_seqs)
         self._lib = host_library()
@@ -194,7 +199,8 @@ class CacheManager:
         arr = c_int * max(n, 1)
         self._h = self._lib.apc_cache_create(
             n, arr(*[g.page_size for g in self.groups]), arr(*[g.num_pages for g in self.groups]),
-            arr(*[(g.window or -1) for g in self.groups]), self.max_seqs)
+            arr(*[(g.window or -1) for g in self.groups]), arr(*[int(g.keep_first) for g in self.groups]),
+            self.max_seqs)
         if not self._h:
             raise CacheError("the cache manager could not be created")
         self._handles: Dict[Hashable, int] = {}      # requests that hold cache -> their number

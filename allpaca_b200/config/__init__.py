@@ -1,5 +1,7 @@
 from .model_config import ConfigError, LlamaConfig, RopeScaling, read_config_json
 from .engine_config import EngineConfig
 from .viresun_config import ViresunConfig
+from .bivatar_config import BivatarConfig
 
-__all__ = ["ConfigError", "LlamaConfig", "RopeScaling", "read_config_json", "EngineConfig", "ViresunConfig"]
+__all__ = ["ConfigError", "LlamaConfig", "RopeScaling", "read_config_json", "EngineConfig", "ViresunConfig",
+           "BivatarConfig"]

@@ -2,15 +2,22 @@
 // query and key, over a paged cache in which a token keeps its key and its value side by
 // side (so keys and values may differ in size), behind an optional sliding window:
 //
-//   score(i, j) = (q_i . k_j) * scale - r1[h] * ln(1 + r2[h] * (i - j))       for 0 <= i - j < window
-//   out_i       = softmax_j(score(i, .)) . v
+//   score(i, j) = (q_i . k_j) * scale - bias_h(i - j)       for 0 <= i - j < window, or j < keep_first
+//   out_i       = softmax_j(score(i, .)) . v * sigmoid(gate[i, h])
 //
-// and the kernel that prepares its operands: every query and key head divided by its root
-// mean square (no weight), queries multiplied by 1 + coef * ln(floor((pos + 1) / every) + 1),
-// keys and values written into the page and slot of their position.
+// bias_h(d) is r1[h] * ln(1 + r2[h] * d) (BIAS_LOG), r1[h] * d (BIAS_LINEAR) or nothing; the first
+// keep_first tokens of a sequence stay visible behind the window, at their true distance; the gate
+// (one 32-bit number per row and head, read from a strided matrix) may be absent.
+//
+// And the kernel that prepares its operands: every query and key head divided by its root
+// mean square (with a weight per coordinate, or none), queries multiplied by
+// 1 + coef * ln(floor((pos + 1) / every) + 1), keys and values written into the page and slot of
+// their position.
 //
 //   q, out : [T, nh, D] and [T, nh, VD]
-//   cache  : one run's pages, [page][nkv][P][D + VD]
+//   cache  : one run's pages, [page][nkv][P][RS]: a token's record of RS numbers holds its key at 0 and
+//            its value at `voff` (side by side: RS = D + VD, voff = D; a value that is the head of the
+//            key, as where queries and outputs live in a latent space all heads share: voff = 0)
 //   block_table : [nseq, max_blocks] page ids; entries the window has passed are never read
 //
 // Scores, softmax, bias and the weighted sum are 32-bit whatever the storage type.  Head
@@ -21,7 +28,22 @@
 #include <float.h>
 
 #define QKN_THREADS 128
-#define MAX_HEAD 256
+#define MAX_HEAD 256              // head sizes the kernels take at full speed (8 value columns per lane)
+#define WIDE_NC 20                // value columns per lane of the kernels built for wider values ...
+#define MAX_WIDE_HEAD (32 * WIDE_NC)   // ... up to 640 (a latent of 512 with 64 rotated dimensions is 576 wide)
+#define BIAS_NONE 0
+#define BIAS_LOG 1
+#define BIAS_LINEAR 2
+
+__device__ __forceinline__ float awb_bias(int kind, float b1, float b2, float dist) {
+    return kind == BIAS_LOG ? b1 * log1pf(b2 * dist) : (kind == BIAS_LINEAR ? b1 * dist : 0.f);
+}
+// Key tiles a row tile walks: the tiles that hold kept first tokens (0 .. tiles_kept-1), then the
+// tiles from the window's first (tile_win) on; where the two meet or overlap, all tiles from 0.
+__device__ __forceinline__ int awb_next_tile(int tile, int tiles_kept, int tile_win) {
+    ++tile;
+    return (tile == tiles_kept && tile < tile_win) ? tile_win : tile;
+}
 
 // one warp per (row, head) of the stacked projection [q heads | k heads | v heads]
 template <typename TI, typename TA>
@@ -29,7 +51,8 @@ __global__ void __launch_bounds__(QKN_THREADS)
 qk_norm_store_kernel(const TI* __restrict__ in, long long ld_in, TA* __restrict__ q_out, TA* __restrict__ cache,
                      const int* __restrict__ positions, const int* __restrict__ token_seq,
                      const int* __restrict__ block_table, int max_blocks, int T, int nh, int nkv, int D, int VD, int P,
-                     size_t page_stride, float eps, int normalise, float temp_coef, int temp_every) {
+                     size_t page_stride, float eps, int normalise, float temp_coef, int temp_every,
+                     const float* __restrict__ qw, const float* __restrict__ kw) {
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * (QKN_THREADS / 32) + (threadIdx.x >> 5);
     const int heads = nh + 2 * nkv;
@@ -53,6 +76,7 @@ qk_norm_store_kernel(const TI* __restrict__ in, long long ld_in, TA* __restrict_
         ss = ap_warp_sum(ss);
         float f = normalise ? 1.0f / sqrtf(ss / (float)D + eps) : 1.0f;
         if (is_q && temp_every > 0) f *= 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f);
+        const float* wv = is_q ? qw : kw;                    // a weight per coordinate, shared by the heads
         TA* dst;
         if (is_q) {
             dst = q_out + ((size_t)t * nh + hh) * D;
@@ -64,7 +88,7 @@ qk_norm_store_kernel(const TI* __restrict__ in, long long ld_in, TA* __restrict_
 #pragma unroll
         for (int i = 0; i < MAX_HEAD / 32; ++i) {
             const int d = lane + 32 * i;
-            if (d < D) dst[d] = ap_from_float<TA>(v[i] * f);
+            if (d < D) dst[d] = ap_from_float<TA>(wv ? v[i] * f * wv[d] : v[i] * f);
         }
     } else {
         if (cache == nullptr) return;
@@ -79,7 +103,8 @@ qk_norm_store_kernel(const TI* __restrict__ in, long long ld_in, TA* __restrict_
 AP_EXPORT int ap_qk_norm_store(const void* in, int in_dtype, long long ld_in, void* q_out, void* cache, int act_dtype,
                                const int* positions, const int* token_seq, const int* block_table, int max_blocks,
                                int T, int nh, int nkv, int D, int VD, int P, long long page_stride, float eps,
-                               int normalise, float temp_coef, int temp_every, cudaStream_t stream) {
+                               int normalise, float temp_coef, int temp_every, const float* qw, const float* kw,
+                               cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && D > 0 && VD > 0 && D <= MAX_HEAD && VD <= MAX_HEAD,
                "qk_norm_store: bad sizes T=%d heads=%d/%d sizes %d/%d (at most %d)", T, nh, nkv, D, VD, MAX_HEAD);
     AP_REQUIRE(cache == nullptr || (token_seq && block_table && max_blocks > 0 && P > 0),
@@ -92,7 +117,8 @@ AP_EXPORT int ap_qk_norm_store(const void* in, int in_dtype, long long ld_in, vo
     AP_CHECK_PDL_LAUNCH("qk_norm_store",                                                                            \
                         ap_launch_pdl(qk_norm_store_kernel<TI, TA>, grid, dim3(QKN_THREADS), 0, stream, (const TI*)in, \
                                       ld_in, (TA*)q_out, (TA*)cache, positions, token_seq, block_table, max_blocks, T, \
-                                      nh, nkv, D, VD, P, (size_t)page_stride, eps, normalise, temp_coef, temp_every))
+                                      nh, nkv, D, VD, P, (size_t)page_stride, eps, normalise, temp_coef, temp_every, \
+                                      qw, kw))
     if (in_dtype == AP_F32 && act_dtype == AP_F32) LAUNCH(float, float);
     else if (in_dtype == AP_F32 && act_dtype == AP_BF16) LAUNCH(float, bf16);
     else if (in_dtype == AP_BF16 && act_dtype == AP_BF16) LAUNCH(bf16, bf16);
@@ -113,13 +139,14 @@ AP_EXPORT int ap_qk_norm_store(const void* in, int in_dtype, long long ld_in, vo
 #define QT (AWB_WARPS * RPW)
 #define KT 32
 
-template <typename TA>
+template <typename TA, int NC>     // NC: value columns per lane the kernel is built for (VD <= 32 NC)
 __global__ void __launch_bounds__(AWB_THREADS)
 attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, const TA* __restrict__ cache,
                              const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_start,
                              const int* __restrict__ positions, int nseq, int nh, int nkv, int D, int VD, int P,
                              size_t page_stride, float scale, int window, const float* __restrict__ r1,
-                             const float* __restrict__ r2, int skip_single) {
+                             const float* __restrict__ r2, int skip_single, int RS, int voff, int bias_kind,
+                             int keep_first, const float* __restrict__ gate, long long gate_ld) {
     extern __shared__ __align__(16) float smem[];
     ap_pdl_trigger();
     ap_pdl_wait();
@@ -152,7 +179,9 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
     }
     const float b1 = r1 ? r1[h] : 0.f, b2 = r2 ? r2[h] : 0.f;
     const int klo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
-    constexpr int NC = MAX_HEAD / 32;
+    // keys 0 .. kfe-1 are kept first tokens that lie before the window of the tile's first row
+    const int kfe = keep_first < klo ? keep_first : klo;
+    const int tiles_kept = (kfe + KT - 1) / KT, tile_win = klo / KT;
     float acc[RPW][NC];
     float m[RPW], l[RPW];
 #pragma unroll
@@ -166,16 +195,18 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
     const int my_rows = min(RPW, nrows - warp * RPW);        // <= 0: this warp only helps loading
     // Key tiles start at multiples of KT whatever the rows of this CTA are: a row then meets its
     // keys in the same tiles and lanes however its prompt was cut, and gets the same bits.  Keys
-    // before klo are not loaded (their pages may have gone back to the pool); no row sees them.
-    for (int k0 = klo / KT * KT; k0 <= pos_last; k0 += KT) {
+    // between the kept first tokens and klo are not loaded (their pages may have gone back to the
+    // pool); no row sees them.
+    for (int tile = tiles_kept > 0 ? 0 : tile_win; tile * KT <= pos_last; tile = awb_next_tile(tile, tiles_kept, tile_win)) {
+        const int k0 = tile * KT;
         __syncthreads();                                     // the tile before is consumed (and q_s is written)
         for (int j = warp; j < KT; j += AWB_WARPS) {
             const int kp = k0 + j;
-            if (kp >= klo && kp <= pos_last) {
+            if ((kp >= klo || kp < kfe) && kp <= pos_last) {
                 const int page = table[kp / P];
-                const TA* src = cache + (size_t)page * page_stride + ((size_t)kvh * P + kp % P) * (D + VD);
+                const TA* src = cache + (size_t)page * page_stride + ((size_t)kvh * P + kp % P) * RS;
                 for (int d = lane; d < D; d += 32) k_s[j * DP + d] = ap_to_float(src[d]);
-                for (int d = lane; d < VD; d += 32) v_s[j * VD + d] = ap_to_float(src[D + d]);
+                for (int d = lane; d < VD; d += 32) v_s[j * VD + d] = ap_to_float(src[voff + d]);
             } else {
                 for (int d = lane; d < D; d += 32) k_s[j * DP + d] = 0.f;
                 for (int d = lane; d < VD; d += 32) v_s[j * VD + d] = 0.f;
@@ -200,9 +231,9 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
         for (int i = 0; i < RPW; ++i) {
             const int qpos = pos_first + warp * RPW + i;
             const int dist = qpos - kp;
-            const bool seen = i < my_rows && dist >= 0 && (window <= 0 || dist < window);
+            const bool seen = i < my_rows && dist >= 0 && (window <= 0 || dist < window || kp < keep_first);
             float sc = -FLT_MAX;
-            if (seen) sc = s[i] * scale - b1 * log1pf(b2 * (float)dist);
+            if (seen) sc = s[i] * scale - awb_bias(bias_kind, b1, b2, (float)dist);
             const float m_new = fmaxf(m[i], ap_warp_max(sc));
             const float p = seen ? expf(sc - m_new) : 0.f;
             const float alpha = expf(m[i] - m_new);
@@ -232,7 +263,8 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
         if (i < my_rows) {
-            const float inv = 1.0f / l[i];
+            float inv = 1.0f / l[i];
+            if (gate) inv /= 1.0f + expf(-gate[(size_t)(row0 + warp * RPW + i) * gate_ld + h]);
             TA* o = out + ((size_t)(row0 + warp * RPW + i) * nh + h) * VD;
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
@@ -274,7 +306,8 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
                                  const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_start,
                                  const int* __restrict__ positions, int nseq, int nh, int nkv, int D, int VD, int P,
                                  size_t page_stride, float scale, int window, const float* __restrict__ r1,
-                                 const float* __restrict__ r2, int skip_single) {
+                                 const float* __restrict__ r2, int skip_single, int RS, int voff, int bias_kind,
+                                 int keep_first, const float* __restrict__ gate, long long gate_ld) {
     __shared__ __align__(16) bf16 k_s[MK][DK + 8];
     __shared__ __align__(16) bf16 vt_s[DV][MK + 8];
     __shared__ float bias_s[MMA_BIAS_TABLE];               // r1 ln(1 + r2 d) for the distances this CTA meets
@@ -320,23 +353,27 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
     const int klo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
     // the largest distance any row of this CTA has to a key it may see
     const int span = pos_last - klo + 1;
-    const bool tabled = r1 != nullptr && span <= MMA_BIAS_TABLE;
+    const bool tabled = bias_kind == BIAS_LOG && span <= MMA_BIAS_TABLE;
     if (tabled)
         for (int d = threadIdx.x; d < span; d += AWB_THREADS) bias_s[d] = b1h * log1pf(b2h * (float)d);
+    const int kfe = keep_first < klo ? keep_first : klo;       // kept first tokens before the first row's window
+    const int tiles_kept = (kfe + MK - 1) / MK, tile_win = klo / MK;
     float o[DV / 8][4];
 #pragma unroll
     for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-FLT_MAX, -FLT_MAX}, l[2] = {0.f, 0.f};
-    const bool vec = D % 8 == 0 && VD % 8 == 0 && page_stride % 8 == 0 && ((uintptr_t)cache & 15) == 0;
+    const bool vec = D % 8 == 0 && VD % 8 == 0 && RS % 8 == 0 && voff % 8 == 0 && page_stride % 8 == 0 &&
+                     ((uintptr_t)cache & 15) == 0;
     const int row_a = warp * 16 + g;                        // this lane's rows: row_a and row_a + 8
-    for (int k0 = klo / MK * MK; k0 <= pos_last; k0 += MK) {
+    for (int tile = tiles_kept > 0 ? 0 : tile_win; tile * MK <= pos_last; tile = awb_next_tile(tile, tiles_kept, tile_win)) {
+        const int k0 = tile * MK;
         __syncthreads();
         for (int idx = threadIdx.x; idx < MK * (DK / 8); idx += AWB_THREADS) {
             const int j = idx / (DK / 8), d0 = (idx - j * (DK / 8)) * 8;
             const int kp = k0 + j;
             uint4 val = make_uint4(0, 0, 0, 0);
-            if (kp >= klo && kp <= pos_last && d0 < D) {
-                const bf16* src = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * (D + VD) + d0;
+            if ((kp >= klo || kp < kfe) && kp <= pos_last && d0 < D) {
+                const bf16* src = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * RS + d0;
                 if (vec) {
                     val = *reinterpret_cast<const uint4*>(src);
                 } else {
@@ -351,8 +388,8 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
             const int j = idx % MK, d0 = (idx / MK) * 8;
             const int kp = k0 + j;
             uint4 val = make_uint4(0, 0, 0, 0);
-            if (kp >= klo && kp <= pos_last && d0 < VD) {
-                const bf16* src = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * (D + VD) + D + d0;
+            if ((kp >= klo || kp < kfe) && kp <= pos_last && d0 < VD) {
+                const bf16* src = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * RS + voff + d0;
                 if (vec) {
                     val = *reinterpret_cast<const uint4*>(src);
                 } else {
@@ -386,10 +423,11 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int r = row_a + (e >> 1) * 8;
-                const int dist = pos_first + r - (k0 + nb * 8 + 2 * t4 + (e & 1));
-                const bool seen = r < nrows && dist >= 0 && (window <= 0 || dist < window);
+                const int kp = k0 + nb * 8 + 2 * t4 + (e & 1);
+                const int dist = pos_first + r - kp;
+                const bool seen = r < nrows && dist >= 0 && (window <= 0 || dist < window || kp < keep_first);
                 float v = -FLT_MAX;
-                if (seen) v = sc[nb][e] * scale - (tabled ? bias_s[dist] : b1h * log1pf(b2h * (float)dist));
+                if (seen) v = sc[nb][e] * scale - ((tabled && dist < span) ? bias_s[dist] : awb_bias(bias_kind, b1h, b2h, (float)dist));
                 sc[nb][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }
@@ -443,7 +481,8 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
     for (int i = 0; i < 2; ++i) {
         const int r = row_a + i * 8;
         if (r >= nrows) continue;
-        const float inv = 1.0f / l[i];
+        float inv = 1.0f / l[i];
+        if (gate) inv /= 1.0f + expf(-gate[(size_t)(row0 + r) * gate_ld + h]);
         bf16* dst = out + ((size_t)(row0 + r) * nh + h) * VD;
 #pragma unroll
         for (int nb = 0; nb < DV / 8; ++nb) {
@@ -458,13 +497,14 @@ template <int DK, int DV>
 static int launch_awb_mma(const void* q, void* out, const void* cache, const int* block_table, int max_blocks,
                           const int* seq_start, const int* positions, int nseq, int T, int nh, int nkv, int D, int VD,
                           int P, long long page_stride, float scale, int window, const float* r1, const float* r2,
-                          int skip_single, cudaStream_t stream) {
+                          int skip_single, int RS, int voff, int bias_kind, int keep_first, const float* gate,
+                          long long gate_ld, cudaStream_t stream) {
     const dim3 grid((unsigned)(T / MQ + nseq), (unsigned)nh);
     AP_CHECK_PDL_LAUNCH("attention_window_bias_mma",
                         ap_launch_pdl(attention_window_bias_mma_kernel<DK, DV>, grid, dim3(AWB_THREADS), 0, stream,
                                       (const bf16*)q, (bf16*)out, (const bf16*)cache, block_table, max_blocks, seq_start,
                                       positions, nseq, nh, nkv, D, VD, P, (size_t)page_stride, scale, window, r1, r2,
-                                      skip_single));
+                                      skip_single, RS, voff, bias_kind, keep_first, gate, gate_ld));
     return AP_OK;
 }
 
@@ -481,13 +521,15 @@ static int launch_awb_mma(const void* q, void* out, const void* cache, const int
 #define DEC_WARPS 8               // the kernel is a chain of dependent steps per key tile: eight warps share the tiles
 #define DEC_THREADS (DEC_WARPS * 32)
 
-template <typename TA, int DEC_REP>   // DEC_REP: query heads per CTA this kernel is built for (1, 2, 4, 8)
+// DEC_REP: query heads per CTA this kernel is built for (1, 2, 4, 8); NC: value columns per lane (VD <= 32 NC)
+template <typename TA, int DEC_REP, int NC>
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ out, const TA* __restrict__ cache,
                                     const int* __restrict__ block_table, int max_blocks,
                                     const int* __restrict__ seq_start, const int* __restrict__ positions, int nh,
                                     int nkv, int D, int VD, int P, size_t page_stride, float scale, int window,
-                                    const float* __restrict__ r1, const float* __restrict__ r2) {
+                                    const float* __restrict__ r1, const float* __restrict__ r2, int RS, int voff,
+                                    int bias_kind, int keep_first, const float* __restrict__ gate, long long gate_ld) {
     constexpr int rep_chunk = DEC_REP;
     extern __shared__ __align__(16) float smem[];
     ap_pdl_trigger();
@@ -499,7 +541,6 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
     const int h0 = kvh * rep_all + blockIdx.z * rep_chunk;      // rep_chunk <= DEC_REP query heads per CTA
     const int rep = min(rep_chunk, rep_all - (int)blockIdx.z * rep_chunk);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int NC = MAX_HEAD / 32;
     float* q_s = smem;                                   // [DEC_REP][D]
     float* p_s = q_s + DEC_REP * D;                      // [DEC_WARPS][DEC_REP][KT]
     float* part = p_s + DEC_WARPS * DEC_REP * KT;        // [DEC_WARPS][DEC_REP][VD + 2]
@@ -526,17 +567,23 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
     }
     const int nc = (VD + 31) / 32;
     float* pw = p_s + warp * DEC_REP * KT;
-    const int first_tile = klo / KT;
-    for (int tile = first_tile + warp; tile * KT <= qpos; tile += DEC_WARPS) {
+    // the tiles of the kept first tokens (0 .. tiles_kept-1), then those from the window's first on
+    const int kfe = keep_first < klo ? keep_first : klo;
+    const int tile_win = klo / KT;
+    const int tiles_kept = min((kfe + KT - 1) / KT, tile_win);
+    const bool vec_ok = sizeof(TA) == 2 && RS % 8 == 0 && voff % 8 == 0 && (page_stride % 8) == 0 &&
+                        ((uintptr_t)cache & 15) == 0;
+    for (int n = warp;; n += DEC_WARPS) {
+        const int tile = n < tiles_kept ? n : tile_win + (n - tiles_kept);
+        if (tile * KT > qpos) break;
         const int kp = tile * KT + lane;
-        const bool seen = kp >= klo && kp <= qpos;
+        const bool seen = (kp >= klo || kp < kfe) && kp <= qpos;
         float s[DEC_REP];
 #pragma unroll
         for (int i = 0; i < DEC_REP; ++i) s[i] = 0.f;
         if (seen) {
-            const TA* kr = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * (D + VD);
-            if (sizeof(TA) == 2 && D % 8 == 0 && (D + VD) % 8 == 0 && (page_stride % 8) == 0 &&
-                ((uintptr_t)cache & 15) == 0) {
+            const TA* kr = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * RS;
+            if (vec_ok && D % 8 == 0) {
                 // eight 16-bit elements of the key's row per load; unrolled far, so that a lane's loads of a
                 // whole row are in flight together
 #pragma unroll 16
@@ -563,7 +610,7 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
         const float dist = (float)(qpos - kp);
 #pragma unroll
         for (int i = 0; i < DEC_REP; ++i) {
-            const float sc = seen ? s[i] * scale - b1[i] * log1pf(b2[i] * dist) : -FLT_MAX;
+            const float sc = seen ? s[i] * scale - awb_bias(bias_kind, b1[i], b2[i], dist) : -FLT_MAX;
             const float m_new = fmaxf(m[i], ap_warp_max(sc));
             const float p = seen ? expf(sc - m_new) : 0.f;
             const float alpha = expf(m[i] - m_new);
@@ -573,11 +620,15 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
 #pragma unroll
             for (int c = 0; c < NC; ++c) acc[i][c] *= alpha;
         }
-        // every lane brings its key's value row into the warp's tile (all loads of a lane in flight at once)
-        if (seen) {
-            const TA* vr = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * (D + VD) + D;
+        // every lane brings its key's value row into the warp's tile (all loads of a lane in flight at once);
+        // a lane whose key no row sees clears its row: its weight is zero, and zero times what was there is not
+        if (!seen) {
             TA* dst = v_s + lane * VDP;
-            if (sizeof(TA) == 2 && D % 8 == 0 && VD % 8 == 0 && (page_stride % 8) == 0 && ((uintptr_t)cache & 15) == 0) {
+            for (int d = 0; d < VD; ++d) dst[d] = ap_from_float<TA>(0.f);
+        } else {
+            const TA* vr = cache + (size_t)table[kp / P] * page_stride + ((size_t)kvh * P + kp % P) * RS + voff;
+            TA* dst = v_s + lane * VDP;
+            if (vec_ok && VD % 8 == 0) {
 #pragma unroll 16
                 for (int d = 0; d < VD; d += 8)
                     *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + d) =
@@ -589,7 +640,7 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
         }
         __syncwarp();
         const int last = min(KT, qpos - tile * KT + 1);
-        for (int j = max(0, klo - tile * KT); j < last; ++j) {
+        for (int j = 0; j < last; ++j) {
             const TA* vr = v_s + j * VDP;
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
@@ -633,7 +684,9 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
             num = fmaf(src[d], f, num);
             den = fmaf(src[VD + 1], f, den);
         }
-        out[((size_t)row * nh + h0 + i) * VD + d] = ap_from_float<TA>(num / den);
+        float res = num / den;
+        if (gate) res /= 1.0f + expf(-gate[(size_t)row * gate_ld + h0 + i]);
+        out[((size_t)row * nh + h0 + i) * VD + d] = ap_from_float<TA>(res);
     }
 }
 
@@ -641,22 +694,36 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
                                        int max_blocks, const int* seq_start, const int* positions, int nseq, int T,
                                        int nh, int nkv, int D, int VD, int P, long long page_stride, float scale,
                                        int window, const float* r1, const float* r2, int single_rows, int other_rows,
-                                       cudaStream_t stream) {
+                                       int RS, int voff, int bias_kind, int keep_first, const float* gate,
+                                       long long gate_ld, cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && nseq >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0 && P > 0 && max_blocks > 0,
                "attention_window_bias: bad sizes T=%d heads=%d kv_heads=%d page=%d", T, nh, nkv, P);
-    AP_REQUIRE(D > 0 && VD > 0 && D <= MAX_HEAD && VD <= MAX_HEAD,
-               "attention_window_bias: head sizes %d/%d are not in 1..%d", D, VD, MAX_HEAD);
+    AP_REQUIRE(D > 0 && VD > 0 && D <= MAX_WIDE_HEAD && VD <= MAX_WIDE_HEAD,
+               "attention_window_bias: head sizes %d/%d are not in 1..%d", D, VD, MAX_WIDE_HEAD);
     AP_REQUIRE(nh <= 65535, "attention_window_bias: %d heads exceed the grid", nh);
-    AP_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attention_window_bias: the bias needs both of its tables");
+    AP_REQUIRE(RS >= D && voff >= 0 && voff + VD <= RS, "attention_window_bias: a record of %d numbers does not hold "
+               "a key of %d and a value of %d at %d", RS, D, VD, voff);
+    AP_REQUIRE(bias_kind == BIAS_NONE || (bias_kind == BIAS_LOG && r1 && r2) || (bias_kind == BIAS_LINEAR && r1),
+               "attention_window_bias: bias kind %d lacks its per-head numbers", bias_kind);
+    AP_REQUIRE(keep_first >= 0 && (gate == nullptr || gate_ld >= nh), "attention_window_bias: bad keep_first or gate stride");
+    if (window <= 0) keep_first = 0;                      // without a window every key is visible anyway
+    if (bias_kind == BIAS_NONE) r1 = r2 = nullptr;
     if (T == 0 || nseq == 0) return AP_OK;
+    const bool wide = VD > MAX_HEAD;                      // more value columns per lane: the kernels built for NC = 20
     // single_rows: sequences that bring one row go to the kernel made for them; other_rows: there are
     // sequences with another number of rows (both 0: everything on the general kernel)
+    // the decode kernel keeps a tile of value rows per warp in shared memory: where the values are too wide
+    // for that, sequences of one row run on the general kernel like the others
+    if (single_rows && (size_t)DEC_WARPS * KT * ((VD + 7) / 8 * 8 + 8) * (dtype == AP_F32 ? 4 : 2) > 160 * 1024) {
+        single_rows = 0;
+        other_rows = 1;
+    }
     if (single_rows) {
         const int rep = nh / nkv;
         // all query heads of a key/value head in one CTA (every key read once) where that still fills the
         // GPU; else fewer heads per CTA and the keys read again from L2
         int rep_chunk = 1;
-        while (rep_chunk < DEC_REP_MAX && rep_chunk < rep) rep_chunk *= 2;
+        while (rep_chunk < (wide ? 2 : DEC_REP_MAX) && rep_chunk < rep) rep_chunk *= 2;
         while (rep_chunk > 1 && (long long)nseq * nkv * ((rep + rep_chunk - 1) / rep_chunk) < 2 * 148) rep_chunk /= 2;
         const dim3 dgrid((unsigned)nseq, (unsigned)nkv, (unsigned)((rep + rep_chunk - 1) / rep_chunk));
         const size_t dsmem = ((size_t)rep_chunk * D + (size_t)DEC_WARPS * rep_chunk * KT +
@@ -665,10 +732,12 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         AP_REQUIRE(nkv <= 65535, "attention_window_bias: %d key/value heads exceed the grid", nkv);
 #define LAUNCH_DEC(TA)                                                                                               \
     do {                                                                                                             \
-        auto kern = rep_chunk == 1 ? attention_window_bias_decode_kernel<TA, 1>                                      \
-                  : rep_chunk == 2 ? attention_window_bias_decode_kernel<TA, 2>                                      \
-                  : rep_chunk == 4 ? attention_window_bias_decode_kernel<TA, 4>                                      \
-                                   : attention_window_bias_decode_kernel<TA, 8>;                                     \
+        auto kern = wide ? (rep_chunk == 1 ? attention_window_bias_decode_kernel<TA, 1, WIDE_NC>                     \
+                                           : attention_window_bias_decode_kernel<TA, 2, WIDE_NC>)                    \
+                  : rep_chunk == 1 ? attention_window_bias_decode_kernel<TA, 1, MAX_HEAD / 32>                       \
+                  : rep_chunk == 2 ? attention_window_bias_decode_kernel<TA, 2, MAX_HEAD / 32>                       \
+                  : rep_chunk == 4 ? attention_window_bias_decode_kernel<TA, 4, MAX_HEAD / 32>                       \
+                                   : attention_window_bias_decode_kernel<TA, 8, MAX_HEAD / 32>;                      \
         if (dsmem > 48 * 1024) {                                                                                     \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsmem);     \
             AP_REQUIRE(e == cudaSuccess, "attention_window_bias: cannot reserve %zu bytes of shared memory", dsmem); \
@@ -676,7 +745,8 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         AP_CHECK_PDL_LAUNCH("attention_window_bias_decode",                                                          \
                             ap_launch_pdl(kern, dgrid, dim3(DEC_THREADS), dsmem, stream, (const TA*)q, (TA*)out,     \
                                           (const TA*)cache, block_table, max_blocks, seq_start, positions, nh, nkv,  \
-                                          D, VD, P, (size_t)page_stride, scale, window, r1, r2));                    \
+                                          D, VD, P, (size_t)page_stride, scale, window, r1, r2, RS, voff, bias_kind, \
+                                          keep_first, gate, gate_ld));                                               \
     } while (0)
         if (dtype == AP_F32) LAUNCH_DEC(float);
         else if (dtype == AP_BF16) LAUNCH_DEC(bf16);
@@ -689,7 +759,7 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         // the tensor-core kernel, built for head sizes rounded up to 32, 64 or 128
         const int dk = D <= 32 ? 32 : (D <= 64 ? 64 : 128), dv = VD <= 32 ? 32 : (VD <= 64 ? 64 : 128);
 #define MMA_ARGS q, out, cache, block_table, max_blocks, seq_start, positions, nseq, T, nh, nkv, D, VD, P, page_stride, \
-                 scale, window, r1, r2, skip_single, stream
+                 scale, window, r1, r2, skip_single, RS, voff, bias_kind, keep_first, gate, gate_ld, stream
         switch (dk * 1000 + dv) {
             case 32032: return launch_awb_mma<32, 32>(MMA_ARGS);
             case 32064: return launch_awb_mma<32, 64>(MMA_ARGS);
@@ -708,7 +778,8 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
     const size_t smem = ((size_t)QT * D + (size_t)KT * (D + 1) + (size_t)KT * VD + AWB_WARPS * RPW * KT) * sizeof(float);
 #define LAUNCH(TA)                                                                                                   \
     do {                                                                                                             \
-        auto kern = attention_window_bias_kernel<TA>;                                                                \
+        auto kern = wide ? attention_window_bias_kernel<TA, WIDE_NC> : attention_window_bias_kernel<TA, MAX_HEAD / 32>; \
+        AP_REQUIRE(smem <= 200 * 1024, "attention_window_bias: head sizes %d/%d do not fit shared memory", D, VD);   \
         if (smem > 48 * 1024) {                                                                                      \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
             AP_REQUIRE(e == cudaSuccess, "attention_window_bias: cannot reserve %zu bytes of shared memory", smem);  \
@@ -716,7 +787,8 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         AP_CHECK_PDL_LAUNCH("attention_window_bias",                                                                 \
                             ap_launch_pdl(kern, grid, dim3(AWB_THREADS), smem, stream, (const TA*)q, (TA*)out,       \
                                           (const TA*)cache, block_table, max_blocks, seq_start, positions, nseq, nh, \
-                                          nkv, D, VD, P, (size_t)page_stride, scale, window, r1, r2, skip_single));  \
+                                          nkv, D, VD, P, (size_t)page_stride, scale, window, r1, r2, skip_single,    \
+                                          RS, voff, bias_kind, keep_first, gate, gate_ld));                          \
     } while (0)
     if (dtype == AP_F32) LAUNCH(float);
     else if (dtype == AP_BF16) LAUNCH(bf16);

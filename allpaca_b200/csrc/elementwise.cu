@@ -169,6 +169,73 @@ AP_EXPORT int ap_add_rmsnorm(float* x, const float* delta, int S, long long delt
 }
 
 // ---------------------------------------------------------------------------
+// The norm on a sublayer's OUTPUT: v = sum_s delta[s, t];  x[t] += mult * rmsnorm(v) * w;
+// copy[t] = x[t] in the activation type, for the sublayer that reads the stream next (may be
+// absent).  Without partial sums (S = 0) only the copy is made.  One CTA per row; the sum of
+// squares and the addition are 32-bit.
+// ---------------------------------------------------------------------------
+template <typename TW, typename TO>
+__global__ void norm_residual_kernel(float* __restrict__ x, const float* __restrict__ delta, int S, size_t delta_stride,
+                                     const TW* __restrict__ w, float eps, float mult, TO* __restrict__ copy, int H) {
+    extern __shared__ __align__(16) float row_buf[];
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    float* xr = x + (size_t)t * H;
+    if (S == 0) {
+        if (copy)
+            for (int i = threadIdx.x; i < H; i += blockDim.x) copy[(size_t)t * H + i] = ap_from_float<TO>(xr[i]);
+        return;
+    }
+    const float* dr = delta + (size_t)t * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = dr[i];
+        for (int s = 1; s < S; ++s) v += dr[(size_t)s * delta_stride + i];
+        row_buf[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = ap_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = xr[i] + mult * (row_buf[i] * inv * ap_to_float(w[i]));
+        xr[i] = v;
+        if (copy) copy[(size_t)t * H + i] = ap_from_float<TO>(v);
+    }
+}
+
+AP_EXPORT int ap_norm_residual(float* x, const float* delta, int S, long long delta_stride, const void* weight,
+                               int w_dtype, float eps, float mult, void* copy, int copy_dtype, int T, int H,
+                               cudaStream_t stream) {
+    AP_REQUIRE(T >= 0 && H > 0 && S >= 0, "norm_residual: bad sizes T=%d H=%d S=%d", T, H, S);
+    AP_REQUIRE(S == 0 || (delta != nullptr && weight != nullptr), "norm_residual: S=%d partial sums but no buffer or weight", S);
+    if (T == 0 || (S == 0 && copy == nullptr)) return AP_OK;
+    const size_t smem = (size_t)H * sizeof(float);
+    AP_REQUIRE(smem <= 200 * 1024, "norm_residual: width %d does not fit the shared-memory row buffer", H);
+    int threads = (H + 31) / 32 * 32;
+    threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
+#define LAUNCH(TW, TO)                                                                                                 \
+    do {                                                                                                               \
+        auto kern = norm_residual_kernel<TW, TO>;                                                                      \
+        if (smem > 48 * 1024) {                                                                                        \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+            AP_REQUIRE(e == cudaSuccess, "norm_residual: cannot reserve %zu bytes of shared memory", smem);            \
+        }                                                                                                              \
+        AP_CHECK_PDL_LAUNCH("norm_residual", ap_launch_pdl(kern, dim3(T), dim3(threads), smem, stream, x, delta, S,    \
+                                                           (size_t)delta_stride, (const TW*)weight, eps, mult,         \
+                                                           (TO*)copy, H));                                             \
+    } while (0)
+    if (w_dtype == AP_F32 && copy_dtype == AP_F32) LAUNCH(float, float);
+    else if (w_dtype == AP_BF16 && copy_dtype == AP_BF16) LAUNCH(bf16, bf16);
+    else if (w_dtype == AP_F32 && copy_dtype == AP_BF16) LAUNCH(float, bf16);
+    else if (w_dtype == AP_BF16 && copy_dtype == AP_F32) LAUNCH(bf16, float);
+    else AP_REQUIRE(false, "norm_residual: unknown dtypes w=%d copy=%d", w_dtype, copy_dtype);
+#undef LAUNCH
+    return AP_OK;
+}
+
+// ---------------------------------------------------------------------------
 // residual add alone: x[t] += sum_s delta[s, t]   (used where no norm follows)
 // ---------------------------------------------------------------------------
 __global__ void residual_add_kernel(float* __restrict__ x, const float* __restrict__ delta, int S,
@@ -281,10 +348,10 @@ __device__ __forceinline__ float load_partial(const TI* in, int S, size_t stride
 }
 
 // cos and sin of pos * inv_freq[i] for every row of the step, computed once and shared by
-// all layers with the same rotation: table[t][i] = (cos, sin).  The angle is a 32-bit
+// all layers with the same rotation: table[t][i] = magnitude * (cos, sin).  The angle is a 32-bit
 // product; sincosf is the accurate (not the fast-math) routine.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  float2* __restrict__ table, int half) {
+                                  float2* __restrict__ table, int half, float magnitude) {
     const int t = blockIdx.x;
     ap_pdl_trigger();
     ap_pdl_wait();
@@ -292,16 +359,16 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float sn, cs;
         sincosf(pos * inv_freq[i], &sn, &cs);
-        table[(size_t)t * half + i] = make_float2(cs, sn);
+        table[(size_t)t * half + i] = make_float2(cs * magnitude, sn * magnitude);
     }
 }
 
 AP_EXPORT int ap_rope_table(const int* positions, const float* inv_freq, float* table, int T, int half,
-                            cudaStream_t stream) {
+                            float magnitude, cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && half > 0, "rope_table: bad sizes T=%d half=%d", T, half);
     if (T == 0) return AP_OK;
     AP_CHECK_PDL_LAUNCH("rope_table", ap_launch_pdl(rope_table_kernel, dim3(T), dim3(half < 128 ? 64 : 128), 0,
-                                                    stream, positions, inv_freq, (float2*)table, half));
+                                                    stream, positions, inv_freq, (float2*)table, half, magnitude));
     return AP_OK;
 }
 

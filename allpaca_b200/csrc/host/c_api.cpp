@@ -30,12 +30,12 @@ APC_EXPORT int apc_pool_held(void* p, int page) { return ((PagePool*)p)->held(pa
 
 // ---- cache manager -----------------------------------------------------------------------
 APC_EXPORT void* apc_cache_create(int ngroups, const int* page_size, const int* num_pages, const int* window,
-                                  int max_seqs) {
+                                  const int* keep_first, int max_seqs) {
     if (ngroups < 0 || max_seqs <= 0) return nullptr;
     std::vector<GroupLayout> groups;
     for (int g = 0; g < ngroups; ++g) {
         if (page_size[g] <= 0 || num_pages[g] <= 0) return nullptr;
-        groups.push_back({page_size[g], num_pages[g], window[g]});
+        groups.push_back({page_size[g], num_pages[g], window[g], keep_first && keep_first[g] > 0 ? keep_first[g] : 0});
     }
     return new CacheManager(groups, max_seqs);
 }

@@ -130,7 +130,9 @@ int CacheManager::release_passed(int64_t req, int* freed) {
         const int64_t first_visible = s.num_tokens - l.window + 1;
         if (first_visible <= 0) continue;
         const int64_t dead = std::min<int64_t>(first_visible / l.page_size, (int64_t)s.tables[g].size());
-        for (int64_t j = 0; j < dead; ++j) {
+        // pages that hold a position below keep_first stay: every later row reads them
+        const int64_t kept = l.keep_first > 0 ? ((int64_t)l.keep_first + l.page_size - 1) / l.page_size : 0;
+        for (int64_t j = kept; j < dead; ++j) {
             if (s.tables[g][j] == kFreed) continue;
             std::string why;
             if (pools_[g].free(s.tables[g][j], &why) != kOk) return fail(kMisuse, why);

@@ -3,7 +3,7 @@
 // Keys and values live in fixed-size pages.  Layers with the same need form a group with a
 // page pool of its own: a group keeps every key of a request, or only a trailing window of
 // them, in which case pages the window has passed go back to the pool while the request is
-// still running.  Each request has, per group, a block table: logical page index -> page id
+// still running (but for the pages that hold a request's first tokens, where the group keeps those).  Each request has, per group, a block table: logical page index -> page id
 // (FREED where the page was given back).  Beside the pages there are slots for per-request
 // state of fixed size, one per running request.
 //
@@ -47,6 +47,7 @@ struct GroupLayout {
     int page_size;
     int num_pages;
     int window;                   // <= 0: keep everything
+    int keep_first = 0;           // with a window: the tokens at positions below this stay readable for good
 };
 
 struct Sequence {

@@ -35,7 +35,9 @@ int Scheduler::add(int64_t id, int64_t prompt_len, int64_t max_tokens, const int
         int64_t need = (longest + layout.page_size - 1) / layout.page_size;
         if (layout.window > 0) {
             // a windowed group keeps at most the window plus one step's rows alive
-            const int64_t span = layout.window + std::min(prefill_chunk_, token_budget_) + layout.page_size;
+            // (and the pages of the first tokens, where the group keeps those)
+            const int64_t span = layout.window + std::min(prefill_chunk_, token_budget_) + layout.page_size +
+                                 (layout.keep_first > 0 ? layout.keep_first + layout.page_size : 0);
             need = std::min(need, (span + layout.page_size - 1) / layout.page_size + 1);
         }
         if (need > layout.num_pages) {
@@ -91,7 +93,8 @@ bool Scheduler::admission_fits(int64_t left) const {
         const GroupLayout& layout = cache_->group(g);
         int64_t tokens = left;
         if (layout.window > 0)
-            tokens = std::min(left, (int64_t)layout.window + std::min(prefill_chunk_, token_budget_) + layout.page_size);
+            tokens = std::min(left, (int64_t)layout.window + std::min(prefill_chunk_, token_budget_) + layout.page_size +
+                                        (layout.keep_first > 0 ? layout.keep_first + layout.page_size : 0));
         const int64_t pages = (tokens + layout.page_size - 1) / layout.page_size;
         if (pages > cache_->num_free_pages(g) - reserved_[g]) return false;
     }

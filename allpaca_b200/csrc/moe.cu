@@ -24,9 +24,12 @@
 #define ACT_SILU 0
 #define ACT_RELU 1
 #define ACT_CLAMPED 2
+#define ACT_GELU_TANH 3
 
 __device__ __forceinline__ float gated_activation(float g, float u, int act, float limit, float alpha, float shift) {
     if (act == ACT_RELU) return fmaxf(g, 0.f) * u;
+    if (act == ACT_GELU_TANH)        // 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) u
+        return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
     if (act == ACT_CLAMPED) {
         g = fminf(g, limit);
         u = fminf(fmaxf(u, -limit), limit);
@@ -53,7 +56,7 @@ __global__ void gated_act_kernel(const TI* __restrict__ in, TO* __restrict__ out
 
 AP_EXPORT int ap_gated_act(const void* in, int in_dtype, void* out, int out_dtype, int T, int I, int pairs, int act,
                            float limit, float alpha, float shift, cudaStream_t stream) {
-    AP_REQUIRE(T >= 0 && I > 0 && act >= 0 && act <= 2, "gated_act: bad sizes T=%d I=%d or activation %d", T, I, act);
+    AP_REQUIRE(T >= 0 && I > 0 && act >= 0 && act <= 3, "gated_act: bad sizes T=%d I=%d or activation %d", T, I, act);
     if (T == 0) return AP_OK;
     long long blocks = ((long long)T * I + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
@@ -422,7 +425,7 @@ static bool moe_few_rows(int pairs, int E, int K, const void* a, const void* w) 
 AP_EXPORT int ap_moe_gate_up(const void* a, int a_dtype, const void* w, int w_dtype, void* y, int y_dtype,
                              const int* perm, int top, const int* tiles, int pairs, int E, int F, int K, int act,
                              float limit, float alpha, float shift, cudaStream_t stream) {
-    AP_REQUIRE(pairs >= 0 && E > 0 && F > 0 && K > 0 && top > 0 && act >= 0 && act <= 2, "moe_gate_up: bad sizes");
+    AP_REQUIRE(pairs >= 0 && E > 0 && F > 0 && K > 0 && top > 0 && act >= 0 && act <= 3, "moe_gate_up: bad sizes");
     if (pairs == 0) return AP_OK;
     const int max_tiles = ap_moe_max_tiles(pairs, E);
     const dim3 grid((unsigned)((F + MOE_BN - 1) / MOE_BN), (unsigned)max_tiles);

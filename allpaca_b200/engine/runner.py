@@ -78,7 +78,7 @@ class ModelRunner:
             # no more than every sequence slot at full length needs
             num_pages = min(num_pages, e.max_num_seqs * -(-self.max_model_len // e.page_size))
         self.num_pages = int(num_pages)
-        layouts = [GroupLayout(e.page_size, self.num_pages, g.need.window) for g in self.cache_plan]
+        layouts = [GroupLayout(e.page_size, self.num_pages, g.need.window, g.need.keep_first) for g in self.cache_plan]
         self.cache = CacheManager(layouts, e.max_num_seqs)
         self.storages = [GroupStorage(len(g.runs), self.num_pages, g.need.page_shape(e.page_size),
                                       g.need.dtype or e.dtype, self.device) for g in self.cache_plan]

@@ -118,6 +118,31 @@ def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Te
          rows.data_ptr() if rows is not None else 0, R, H, stream_handle())
 
 
+def norm_residual(x: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+                  mult: float, copy: Optional[torch.Tensor] = None) -> None:
+    """The norm on a sublayer's output: ``x += mult * rmsnorm(sum(delta)) * weight`` in 32-bit, and
+    ``copy = x`` in ``copy``'s type for whoever reads the stream next (None: no copy).  With
+    ``delta`` None only the copy is made."""
+    _check(x, "x", torch.float32, 2)
+    T, H = x.shape
+    S, dptr, dstride = 0, 0, 0
+    if delta is not None:
+        dptr, code, S, dstride, dT, dN = _partials(delta, "delta")
+        if code != AP_F32 or dT != T or dN != H:
+            raise KernelError(f"norm_residual: delta {tuple(delta.shape)} {delta.dtype} does not match x {tuple(x.shape)}")
+        _check(weight, "weight", dims=1)
+        if weight.shape[0] != H:
+            raise KernelError("norm_residual: the weight must have one entry per column")
+    if copy is not None:
+        _check(copy, "copy", dims=2)
+        if tuple(copy.shape) != (T, H):
+            raise KernelError("norm_residual: the copy must have the stream's shape")
+    call(core(), "ap_norm_residual", x.data_ptr(), dptr, S, dstride, weight.data_ptr() if delta is not None else 0,
+         dtype_code(weight.dtype) if delta is not None else AP_F32, float(eps), float(mult),
+         copy.data_ptr() if copy is not None else 0, dtype_code(copy.dtype) if copy is not None else AP_F32, T, H,
+         stream_handle())
+
+
 def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
     """``x += sum(delta)`` in 32-bit."""
     _check(x, "x", torch.float32, 2)
@@ -191,8 +216,8 @@ def clear_page_tails(pages: torch.Tensor, page_size_dim: int, positions: torch.T
          block_table.data_ptr(), block_table.shape[1], context_lens.data_ptr(), positions.shape[0], stream_handle())
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, table: torch.Tensor) -> None:
-    """``table[t, i] = (cos, sin)(positions[t] * inv_freq[i])`` with a 32-bit angle."""
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, table: torch.Tensor, magnitude: float = 1.0) -> None:
+    """``table[t, i] = magnitude * (cos, sin)(positions[t] * inv_freq[i])`` with a 32-bit angle."""
     _check(positions, "positions", torch.int32, 1)
     _check(inv_freq, "inv_freq", torch.float32, 1)
     _check(table, "table", torch.float32, 3)
@@ -200,7 +225,7 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, table: torch.Ten
     if tuple(table.shape) != (T, half, 2):
         raise KernelError("rope_table: table must be [T, head_dim/2, 2]")
     call(core(), "ap_rope_table", positions.data_ptr(), inv_freq.data_ptr(), table.data_ptr(), T, half,
-         stream_handle())
+         float(magnitude), stream_handle())
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, pairs: bool = False) -> None:
@@ -729,7 +754,7 @@ def check_kernel_status() -> None:
 
 
 from .mixers import (attention_window_bias, causal_conv_silu, embed_sinusoid_norm, gated_group_rmsnorm,  # noqa: E402
-                     qk_norm_store, ssm_scan)
+                     head_project, latent_prepare, qk_norm_store, ssm_scan)
 from . import routed  # noqa: E402,F401
 from .routed import (gated_act, moe_combine, moe_down, moe_gate_up, moe_gather, moe_max_tiles,  # noqa: E402
                      moe_route, moe_route_rows, moe_sort)

@@ -29,7 +29,9 @@ _CORE_SIGNATURES = {
     "ap_residual_add": [_P, _P, _I, _L, _L, _P],
     "ap_rope_kv_store": [_P, _I, _I, _L, _P, _P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _L, _P],
     "ap_clear_page_tails": [_P, _I, _L, _L, _I, _I, _I, _I, _P, _P, _P, _I, _P, _I, _P],
-    "ap_rope_table": [_P, _P, _P, _I, _I, _P],
+    "ap_rope_table": [_P, _P, _P, _I, _I, _F, _P],
+    # int ap_norm_residual(x, delta, S, delta_stride, weight, w_dtype, eps, mult, copy, copy_dtype, T, H, stream)
+    "ap_norm_residual": [_P, _P, _I, _L, _P, _I, _F, _F, _P, _I, _I, _I, _P],
     "ap_swiglu": [_P, _I, _I, _L, _P, _I, _I, _I, _I, _P],
     "ap_gemm_simt": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _L, _L, _L, _P],
     "ap_argmax": [_P, _L, _I, _I, _P, _P],
@@ -40,12 +42,20 @@ _CORE_SIGNATURES = {
     #                            x, T, H, V, stream)
     "ap_embed_sinusoid_norm": [_P, _P, _P, _I, _P, _P, _I, _F, _F, _P, _I, _I, _I, _P],
     # int ap_qk_norm_store(in, in_dtype, ld_in, q_out, cache, act_dtype, positions, token_seq, block_table,
-    #                      max_blocks, T, nh, nkv, D, VD, P, page_stride, eps, normalise, temp_coef, temp_every, stream)
-    "ap_qk_norm_store": [_P, _I, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _F, _I, _P],
+    #                      max_blocks, T, nh, nkv, D, VD, P, page_stride, eps, normalise, temp_coef, temp_every,
+    #                      q_weight, k_weight, stream)
+    "ap_qk_norm_store": [_P, _I, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _F, _I, _P, _P, _P],
     # int ap_attention_window_bias(q, out, cache, dtype, block_table, max_blocks, seq_start, positions, nseq, T,
-    #                              nh, nkv, D, VD, P, page_stride, scale, window, r1, r2, single_rows, other_rows, stream)
+    #                              nh, nkv, D, VD, P, page_stride, scale, window, r1, r2, single_rows, other_rows,
+    #                              record, value_offset, bias_kind, keep_first, gate, gate_ld, stream)
     "ap_attention_window_bias": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P, _I, _I,
-                                 _P],
+                                 _I, _I, _I, _I, _P, _L, _P],
+    # int ap_latent_prepare(in, ld, q0, Q, q_weight, cq, kv0, R, rot, rot_dims, kv_weight, cache, act_dtype, positions,
+    #                       token_seq, block_table, max_blocks, P, page_stride, cos_sin, eps, T, stream)
+    "ap_latent_prepare": [_P, _L, _I, _I, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _L, _P, _F, _I, _P],
+    # int ap_head_project(in, in_dtype, in_ld, in_hs, w, w_dtype, out, out_dtype, out_ld, out_hs, T, H, K, N, tail,
+    #                     tail_dims, cos_sin, stream)
+    "ap_head_project": [_P, _I, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     # int ap_causal_conv_silu(in, ld_in, col0, w, bias, state, state_stride, token_seq, seq_start, positions,
     #                         state_slots, out, T, nseq, C, taps, stream)
     "ap_causal_conv_silu": [_P, _L, _I, _P, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],

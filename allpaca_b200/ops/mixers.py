@@ -39,13 +39,18 @@ def embed_sinusoid_norm(tokens: torch.Tensor, positions: torch.Tensor, table: to
          x.data_ptr(), T, H, table.shape[0], stream_handle())
 
 
-def _kv_pages(cache_layer: torch.Tensor, num_kv_heads: int, key_dim: int, value_dim: int, name: str):
-    """(P, page stride) of pages ``[pages, nkv, P, key_dim + value_dim]``."""
-    if cache_layer.dim() != 4 or cache_layer.shape[1] != num_kv_heads or cache_layer.shape[3] != key_dim + value_dim:
-        raise KernelError(f"{name}: pages {tuple(cache_layer.shape)} are not [pages, {num_kv_heads}, P, "
-                          f"{key_dim} + {value_dim}]")
-    if cache_layer.stride(3) != 1 or cache_layer.stride(2) != key_dim + value_dim \
-            or cache_layer.stride(1) != cache_layer.shape[2] * (key_dim + value_dim):
+BIAS_KINDS = {None: 0, "log": 1, "linear": 2}
+
+
+def _kv_pages(cache_layer: torch.Tensor, num_kv_heads: int, record: int, name: str):
+    """(P, page stride) of pages ``[pages, nkv, P, record]``; with one key/value head the pages may
+    come as ``[pages, P, record]``."""
+    if cache_layer.dim() == 3 and num_kv_heads == 1:
+        cache_layer = cache_layer.unsqueeze(1)
+    if cache_layer.dim() != 4 or cache_layer.shape[1] != num_kv_heads or cache_layer.shape[3] != record:
+        raise KernelError(f"{name}: pages {tuple(cache_layer.shape)} are not [pages, {num_kv_heads}, P, {record}]")
+    if cache_layer.stride(3) != 1 or cache_layer.stride(2) != record \
+            or (num_kv_heads > 1 and cache_layer.stride(1) != cache_layer.shape[2] * record):
         raise KernelError(f"{name}: a page must be contiguous")
     return cache_layer.shape[2], cache_layer.stride(0)
 
@@ -53,16 +58,25 @@ def _kv_pages(cache_layer: torch.Tensor, num_kv_heads: int, key_dim: int, value_
 def qk_norm_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[torch.Tensor],
                   positions: torch.Tensor, token_seq: torch.Tensor, block_table: Optional[torch.Tensor],
                   num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, eps: float,
-                  normalise: bool = True, temp_coef: float = 0.0, temp_every: int = 0) -> None:
+                  normalise: bool = True, temp_coef: float = 0.0, temp_every: int = 0,
+                  q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None) -> None:
     """Prepare the operands of :func:`attention_window_bias` from the stacked projection
-    ``qkv [T, nh*D + nkv*D + nkv*VD]``: every query and key head rescaled to unit mean square
-    (``normalise``), queries multiplied by ``1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)``
-    (``temp_every`` 0: no temperature) into ``q_out [T, nh*D]``, keys and values into the pages
-    ``cache_layer [pages, nkv, P, D + VD]`` (None: not stored)."""
-    _check(qkv, "qkv", dims=2)
+    ``qkv [T, nh*D + nkv*D + nkv*VD (+ more columns that are not read)]``: every query and key head
+    rescaled to unit mean square (``normalise``) and multiplied by ``q_weight`` / ``k_weight``
+    (32-bit ``[D]``, shared by the heads; None: no weight), queries multiplied by
+    ``1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)`` (``temp_every`` 0: no temperature) into
+    ``q_out [T, nh*D]``, keys and values into the pages ``cache_layer [pages, nkv, P, D + VD]``
+    (None: not stored)."""
+    if qkv.dim() != 2 or not qkv.is_cuda or qkv.stride(1) != 1:
+        raise KernelError("qk_norm_store: qkv must be a CUDA matrix with contiguous rows")
     _check(q_out, "q_out", dims=2)
     T = qkv.shape[0]
-    if qkv.shape[1] != (num_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim \
+    for w, n in ((q_weight, "q_weight"), (k_weight, "k_weight")):
+        if w is not None:
+            _check(w, n, torch.float32, 1)
+            if w.shape[0] != key_dim:
+                raise KernelError(f"qk_norm_store: {n} must have one entry per coordinate of a head")
+    if qkv.shape[1] < (num_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim \
             or q_out.shape[0] < T or q_out.shape[1] != num_heads * key_dim:
         raise KernelError(f"qk_norm_store: shapes disagree: qkv {tuple(qkv.shape)}, q_out {tuple(q_out.shape)}")
     _check(positions, "positions", torch.int32, 1)
@@ -70,7 +84,7 @@ def qk_norm_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[
     if cache_layer is not None:
         if cache_layer.dtype != q_out.dtype:
             raise KernelError("qk_norm_store: the pages must have the queries' type")
-        P, page_stride = _kv_pages(cache_layer, num_kv_heads, key_dim, value_dim, "qk_norm_store")
+        P, page_stride = _kv_pages(cache_layer, num_kv_heads, key_dim + value_dim, "qk_norm_store")
         _check(token_seq, "token_seq", torch.int32, 1)
         _check(block_table, "block_table", torch.int32, 2)
         cptr, tsptr, btptr, maxb = cache_layer.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), \
@@ -78,6 +92,7 @@ def qk_norm_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[
     call(core(), "ap_qk_norm_store", qkv.data_ptr(), dtype_code(qkv.dtype), qkv.stride(0), q_out.data_ptr(), cptr,
          dtype_code(q_out.dtype), positions.data_ptr(), tsptr, btptr, maxb, T, num_heads, num_kv_heads, key_dim,
          value_dim, P, page_stride, float(eps), 1 if normalise else 0, float(temp_coef), int(temp_every),
+         q_weight.data_ptr() if q_weight is not None else 0, k_weight.data_ptr() if k_weight is not None else 0,
          stream_handle())
 
 
@@ -85,10 +100,18 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
                           seq_start: torch.Tensor, positions: torch.Tensor, num_seqs: int, num_heads: int,
                           num_kv_heads: int, key_dim: int, value_dim: int, scale: float, window: int = 0,
                           r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None,
-                          single_rows: bool = False, other_rows: bool = True) -> None:
-    """Causal attention of ``q [T, nh*D]`` over pages ``[pages, nkv, P, D + VD]`` into
-    ``out [T, nh*VD]``: ``score = q.k * scale - r1[h] * ln(1 + r2[h] * distance)`` (``r1``, ``r2``
-    32-bit ``[nh]`` or None), over the last ``window`` keys (0: all), ordinary softmax, 32-bit.
+                          single_rows: bool = False, other_rows: bool = True, bias: Optional[str] = "log",
+                          keep_first: int = 0, gate: Optional[torch.Tensor] = None,
+                          record: Optional[int] = None, value_offset: Optional[int] = None) -> None:
+    """Causal attention of ``q [T, nh*D]`` over pages ``[pages, nkv, P, record]`` into
+    ``out [T, nh*VD]``: ``score = q.k * scale - bias_h(distance)``, over the last ``window`` keys (0: all)
+    and, behind a window, the sequence's first ``keep_first`` tokens; ordinary softmax, 32-bit.
+
+    ``bias``: ``"log"``: ``r1[h] * ln(1 + r2[h] * distance)``; ``"linear"``: ``r1[h] * distance``; None: no
+    bias (``r1``, ``r2`` 32-bit ``[nh]``; without ``r1`` there is no bias whatever ``bias`` says).
+    ``gate`` (32-bit ``[T, nh]``, may be a strided view): head ``h`` of row ``t`` is multiplied by
+    ``sigmoid(gate[t, h])``.  A token's record holds its key at 0 and its value at ``value_offset``
+    (default: side by side, ``record = D + VD`` and ``value_offset = D``).
 
     ``single_rows``: sequences that bring one row run on the kernel made for decoding (the query
     heads of a key/value head together, the key tiles spread over the warps); ``other_rows`` says
@@ -101,7 +124,19 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
         raise KernelError("attention_window_bias: q/out do not match the heads")
     if cache_layer.dtype != q.dtype:
         raise KernelError("attention_window_bias: the pages must have the queries' type")
-    P, page_stride = _kv_pages(cache_layer, num_kv_heads, key_dim, value_dim, "attention_window_bias")
+    record = key_dim + value_dim if record is None else int(record)
+    value_offset = key_dim if value_offset is None else int(value_offset)
+    P, page_stride = _kv_pages(cache_layer, num_kv_heads, record, "attention_window_bias")
+    if r1 is None:
+        bias = None
+    if bias not in BIAS_KINDS:
+        raise KernelError(f"attention_window_bias: bias {bias!r} is not known (log, linear, None)")
+    gptr, gld = 0, 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.dim() != 2 or gate.shape[0] < T or gate.shape[1] != num_heads \
+                or gate.stride(1) != 1 or not gate.is_cuda:
+            raise KernelError("attention_window_bias: the gate must be 32-bit [T, heads] with contiguous rows")
+        gptr, gld = gate.data_ptr(), gate.stride(0)
     _check(block_table, "block_table", torch.int32, 2)
     _check(seq_start, "seq_start", torch.int32, 1)
     _check(positions, "positions", torch.int32, 1)
@@ -116,7 +151,79 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
          block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(), positions.data_ptr(), int(num_seqs), T,
          num_heads, num_kv_heads, key_dim, value_dim, P, page_stride, float(scale), int(window or 0),
          r1.data_ptr() if r1 is not None else 0, r2.data_ptr() if r2 is not None else 0,
-         1 if single_rows else 0, 1 if other_rows else 0, stream_handle())
+         1 if single_rows else 0, 1 if other_rows else 0, record, value_offset, BIAS_KINDS[bias], int(keep_first or 0),
+         gptr, gld, stream_handle())
+
+
+def latent_prepare(proj: torch.Tensor, q_col: int, q_rank: int, q_weight: Optional[torch.Tensor],
+                   q_latent: Optional[torch.Tensor], kv_col: int, kv_rank: int, rot_dim: int, rot_dims: int,
+                   kv_weight: Optional[torch.Tensor], cache_layer: Optional[torch.Tensor], positions: torch.Tensor,
+                   token_seq: torch.Tensor, block_table: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
+                   eps: float) -> None:
+    """From the stacked down-projections ``proj [T, ...]`` (32-bit): columns ``q_col .. q_col + q_rank``
+    RMS-normed with ``q_weight`` into ``q_latent [T, q_rank]``; columns ``kv_col .. kv_col + kv_rank``
+    RMS-normed with ``kv_weight`` and the ``rot_dim`` columns behind them rotated (the first ``rot_dims``
+    of them, entry ``i`` paired with ``i + rot_dims/2``, by ``cos_sin [T, rot_dims/2, 2]``) into the
+    row's page and slot of ``cache_layer [pages, P, kv_rank + rot_dim]`` (None: not stored)."""
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1 or not proj.is_cuda:
+        raise KernelError("latent_prepare: proj must be a 32-bit CUDA matrix with contiguous rows")
+    T = proj.shape[0]
+    qptr = qwptr = cptr = kvwptr = tsptr = btptr = csptr = 0
+    P, page_stride, maxb, act = 1, 0, 0, None
+    if q_rank > 0:
+        _check(q_latent, "q_latent", dims=2)
+        _check(q_weight, "q_weight", torch.float32, 1)
+        if tuple(q_latent.shape) != (T, q_rank) or q_weight.shape[0] != q_rank or q_col + q_rank > proj.shape[1]:
+            raise KernelError("latent_prepare: the query latent's shapes disagree")
+        qptr, qwptr, act = q_latent.data_ptr(), q_weight.data_ptr(), q_latent.dtype
+    if cache_layer is not None:
+        _check(kv_weight, "kv_weight", torch.float32, 1)
+        if kv_weight.shape[0] != kv_rank or kv_col + kv_rank + rot_dim > proj.shape[1]:
+            raise KernelError("latent_prepare: the key/value latent's shapes disagree")
+        if act is not None and cache_layer.dtype != act:
+            raise KernelError("latent_prepare: the pages must have the query latent's type")
+        act = cache_layer.dtype
+        P, page_stride = _kv_pages(cache_layer, 1, kv_rank + rot_dim, "latent_prepare")
+        _check(token_seq, "token_seq", torch.int32, 1)
+        _check(block_table, "block_table", torch.int32, 2)
+        cptr, kvwptr, tsptr, btptr, maxb = cache_layer.data_ptr(), kv_weight.data_ptr(), token_seq.data_ptr(), \
+            block_table.data_ptr(), block_table.shape[1]
+        if rot_dims > 0:
+            _check(cos_sin, "cos_sin", torch.float32, 3)
+            if tuple(cos_sin.shape) != (T, rot_dims // 2, 2):
+                raise KernelError("latent_prepare: cos_sin must be [T, rot_dims/2, 2]")
+            csptr = cos_sin.data_ptr()
+    if act is None:
+        return
+    _check(positions, "positions", torch.int32, 1)
+    call(core(), "ap_latent_prepare", proj.data_ptr(), proj.stride(0), int(q_col), int(q_rank), qwptr, qptr,
+         int(kv_col), int(kv_rank), int(rot_dim), int(rot_dims), kvwptr, cptr, dtype_code(act), positions.data_ptr(),
+         tsptr, btptr, maxb, P, page_stride, csptr, float(eps), T, stream_handle())
+
+
+def head_project(inp: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int, tail: int = 0,
+                 tail_dims: int = 0, cos_sin: Optional[torch.Tensor] = None) -> None:
+    """``out[t, h, :N] = inp[t, h, :K] @ weight[h]`` for ``weight [heads, K, N]``, every sum 32-bit in
+    ascending ``k``.  ``inp [T, heads*(K + tail)]`` and ``out [T, heads*(N + tail)]``: the ``tail``
+    numbers behind a head's ``K`` inputs go behind its ``N`` outputs, the first ``tail_dims`` of them
+    rotated by ``cos_sin [T, tail_dims/2, 2]`` (entry ``i`` paired with ``i + tail_dims/2``)."""
+    _check(inp, "inp", dims=2)
+    _check(weight, "weight", dims=3)
+    _check(out, "out", dims=2)
+    T = inp.shape[0]
+    H, K, N = weight.shape
+    if H != heads or inp.shape[1] != H * (K + tail) or tuple(out.shape) != (T, H * (N + tail)):
+        raise KernelError(f"head_project: inp {tuple(inp.shape)}, weight {tuple(weight.shape)} and out "
+                          f"{tuple(out.shape)} disagree (tail {tail})")
+    csptr = 0
+    if tail_dims > 0:
+        _check(cos_sin, "cos_sin", torch.float32, 3)
+        if tuple(cos_sin.shape) != (T, tail_dims // 2, 2):
+            raise KernelError("head_project: cos_sin must be [T, tail_dims/2, 2]")
+        csptr = cos_sin.data_ptr()
+    call(core(), "ap_head_project", inp.data_ptr(), dtype_code(inp.dtype), inp.stride(0), K + tail, weight.data_ptr(),
+         dtype_code(weight.dtype), out.data_ptr(), dtype_code(out.dtype), out.stride(0), N + tail, T, H, K, N,
+         int(tail), int(tail_dims), csptr, stream_handle())
 
 
 def causal_conv_silu(inp: torch.Tensor, col0: int, weight: torch.Tensor, bias: Optional[torch.Tensor],

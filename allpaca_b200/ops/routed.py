@@ -8,7 +8,7 @@ import torch
 
 from . import KernelError, _check, call, core, dtype_code, stream_handle
 
-ACTIVATIONS = {"silu": 0, "relu": 1, "clamped_sigmoid": 2}
+ACTIVATIONS = {"silu": 0, "relu": 1, "clamped_sigmoid": 2, "gelu_tanh": 3}
 
 
 def activation_code(name: str) -> int:
@@ -23,7 +23,7 @@ def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu"
     """``out[t, j] = act(gate, up)`` for ``gate_up [T, 2I]`` holding ``[gate | up]`` (or, with
     ``pairs``, gate and up columns alternating).  ``silu``: ``silu(g) u``; ``relu``: ``max(g, 0) u``;
     ``clamped_sigmoid``: ``g' sigmoid(alpha g') (u' + shift)`` with ``g' = min(g, limit)`` and
-    ``u' = clamp(u, -limit, limit)``."""
+    ``u' = clamp(u, -limit, limit)``; ``gelu_tanh``: ``0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) u``."""
     _check(gate_up, "gate_up", dims=2)
     _check(out, "out", dims=2)
     T, inter = out.shape

@@ -1,0 +1,135 @@
+"""Attention whose keys and values are projections of one small latent vector per token.
+
+With ``h`` the mixer's input, ``H`` heads, per head ``head_dim`` unrotated and ``rot_dim`` rotated
+query/key dimensions, values of ``value_dim`` and a latent of ``kv_rank``:
+
+* queries pass through a latent of their own: ``c_q = rmsnorm(W_dq h)`` (weight ``dq.norm``),
+  ``q = W_uq c_q``, head by head ``[head_dim unrotated | rot_dim rotated]``;
+* ``W_dkv h`` has ``kv_rank + rot_dim`` rows: the first ``kv_rank``, RMS-normed (weight ``dkv.norm``), are
+  the latent ``c``; the last ``rot_dim``, not normed, are one rotated key part all heads share;
+* head ``a`` has the unrotated key ``W_uk[a] c`` and the value ``W_uv[a] c``;
+  ``score = (q_unrotated . k_unrotated + q_rotated . k_rotated) * scale``, causal, ordinary softmax;
+* the rotation (``rope``: ``dims``, ``theta``, ``scaling``, see :mod:`.rope`) acts on the first ``dims`` of
+  the ``rot_dim`` rotated dimensions of queries and of the shared key part, never on values;
+* ``output_gate``: head ``a`` of the result is multiplied by ``sigmoid(W_g h)_a`` before ``W_o``;
+* ``shares_latent``: the layer has no ``W_dkv`` and reads the latent and the rotated key part another
+  layer's run keeps (the model's order names that run as this run's ``cache_from``), with its own
+  ``W_uk``, ``W_uv``, queries and everything else.
+
+A token keeps ``[c | rotated key part]`` in its page and nothing per head.  The kernels never form the
+per-head keys and values: since ``q . (W_uk[a] c) = (W_uk[a]^T q) . c`` and
+``sum_j p_j W_uv[a] c_j = W_uv[a] sum_j p_j c_j``, queries are carried into the latent space, the
+attention runs there with ONE key/value head whose value is the head of its key's record, and its
+result is carried out through ``W_uv``.  Norms, angles, scores, softmax, gate and all sums are 32-bit.
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from .. import ops
+from .base import BuildEnv, CacheNeed, LayerCache, Mixer, PartError, PartSpec, WeightSpec, build, register
+from .linear import Linear
+
+
+@register("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    """Parameters: ``hidden_size``, ``num_heads``, ``head_dim``, ``rot_dim``, ``value_dim``, ``kv_rank``,
+    ``q_rank``, ``scale``, ``norm_eps``, ``rope`` (``{"dims", "theta", "scaling"}``), ``output_gate``,
+    ``shares_latent``; tensors ``dq``, ``dq.norm``, ``uq``, ``dkv``, ``dkv.norm`` (both absent with
+    ``shares_latent``), ``uk``, ``uv``, ``g`` (with ``output_gate``), ``o``."""
+
+    MAX_RECORD = 640            # widest [latent | rotated part] the attention kernels take
+
+    def __init__(self, params, env: BuildEnv):
+        super().__init__(params, env)
+        self.require("hidden_size", "num_heads", "head_dim", "rot_dim", "value_dim", "kv_rank", "q_rank", "scale",
+                     "norm_eps")
+        p = params
+        self.hidden, self.nh = int(p["hidden_size"]), int(p["num_heads"])
+        self.hd, self.rot, self.vd = int(p["head_dim"]), int(p["rot_dim"]), int(p["value_dim"])
+        self.R, self.Q = int(p["kv_rank"]), int(p["q_rank"])
+        self.scale, self.eps = float(p["scale"]), float(p["norm_eps"])
+        self.output_gate = bool(p.get("output_gate", False))
+        self.shares_latent = bool(p.get("shares_latent", False))
+        if min(self.nh, self.hd, self.vd, self.R, self.Q) <= 0 or self.rot < 0:
+            raise PartError("latent attention needs positive sizes")
+        if self.R + self.rot > self.MAX_RECORD:
+            raise PartError(f"a latent of {self.R} with {self.rot} rotated dimensions is wider than the "
+                            f"attention kernels take ({self.MAX_RECORD})")
+        rope = p.get("rope")
+        self.rope = None
+        self.rot_dims = 0
+        if rope and self.rot > 0:
+            self.rot_dims = int(rope["dims"])
+            if self.rot_dims % 2 or not (0 < self.rot_dims <= self.rot):
+                raise PartError(f"{self.rot_dims} rotated dimensions do not fit a rotated part of {self.rot}")
+            self.rope = build("position", PartSpec("rope", {
+                "head_dim": self.rot_dims, "theta": float(rope["theta"]), "scaling": rope.get("scaling"),
+                "pairing": "half"}), env)
+        self.kv_size = 0 if self.shares_latent else self.R + self.rot
+        self.g_size = self.nh if self.output_gate else 0
+        # one product for everything that reads the mixer's input: [dq | dkv | g]
+        self.down = Linear(env, self.Q + self.kv_size + self.g_size, self.hidden)
+        self.uq = Linear(env, self.nh * (self.hd + self.rot), self.Q)
+        self.o = Linear(env, self.hidden, self.nh * self.vd)
+        self.uk = self.uv = self.q_weight = self.kv_weight = None
+
+    def weights(self) -> Dict[str, WeightSpec]:
+        w = {"dq": WeightSpec((self.Q, self.hidden)), "dq.norm": WeightSpec((self.Q,), "norm"),
+             "uq": WeightSpec((self.nh * (self.hd + self.rot), self.Q)),
+             "uk": WeightSpec((self.nh * self.hd, self.R)), "uv": WeightSpec((self.nh * self.vd, self.R)),
+             "o": WeightSpec((self.hidden, self.nh * self.vd))}
+        if not self.shares_latent:
+            w["dkv"] = WeightSpec((self.R + self.rot, self.hidden))
+            w["dkv.norm"] = WeightSpec((self.R,), "norm")
+        if self.output_gate:
+            w["g"] = WeightSpec((self.nh, self.hidden))
+        return w
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        stacked = [tensors["dq"]] + ([] if self.shares_latent else [tensors["dkv"]]) \
+            + ([tensors["g"]] if self.output_gate else [])
+        self.down.load(torch.cat(stacked, dim=0))
+        self.uq.load(tensors["uq"])
+        self.o.load(tensors["o"])
+        # per head: [head_dim, kv_rank] carries a query into the latent space as it is stored;
+        # [kv_rank, value_dim] (the stored matrix transposed) carries a latent result out
+        self.uk = tensors["uk"].view(self.nh, self.hd, self.R).contiguous()
+        self.uv = tensors["uv"].view(self.nh, self.vd, self.R).transpose(1, 2).contiguous()
+        self.q_weight = tensors["dq.norm"].float().contiguous()
+        if not self.shares_latent:
+            self.kv_weight = tensors["dkv.norm"].float().contiguous()
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return CacheNeed(outer=(), inner=(self.R + self.rot,))
+
+    def forward(self, h: torch.Tensor, step, cache: LayerCache) -> torch.Tensor:
+        T = h.shape[0]
+        ws = self.env.workspace
+        dt = self.env.dtype
+        if cache.writes == self.shares_latent:
+            raise PartError("a latent attention layer writes pages exactly when it has a down-projection of its own")
+        proj = self.down.forward(h, "lattn.down", "float32")
+        cos_sin = self.rope.rotation_for(step)[0] if self.rope is not None else None
+        table = step.block_tables[cache.group]
+        cq = ws.get("lattn.cq", (T, self.Q), dt)
+        ops.latent_prepare(proj, 0, self.Q, self.q_weight, cq, self.Q, self.R, self.rot, self.rot_dims,
+                           self.kv_weight, cache.pages if cache.writes else None, step.positions, step.token_seq,
+                           table, cos_sin, self.eps)
+        q = self.uq.forward(cq, "lattn.q", "float32")
+        rec = self.R + self.rot
+        qa = ws.get("lattn.qa", (T, self.nh * rec), dt)
+        ops.head_project(q, self.uk, qa, self.nh, tail=self.rot, tail_dims=self.rot_dims, cos_sin=cos_sin)
+        gate = proj[:, self.Q + self.kv_size:] if self.output_gate else None
+        ol = ws.get("lattn.ol", (T, self.nh * self.R), dt)
+        lens = step.host_query_lens
+        single = dt == torch.bfloat16 and (step.max_query_len == 1 or 1 in lens)
+        ops.attention_window_bias(qa, ol, cache.pages, table, step.seq_start, step.positions, step.num_seqs,
+                                  self.nh, 1, rec, self.R, self.scale, 0, None, None, single_rows=single,
+                                  other_rows=step.max_query_len != 1, bias=None, gate=gate, record=rec,
+                                  value_offset=0)
+        ov = ws.get("lattn.ov", (T, self.nh * self.vd), dt)
+        ops.head_project(ol, self.uv, ov, self.nh)
+        return self.o.forward(ov, "lattn.o", "delta")

@@ -133,13 +133,15 @@ class CacheNeed:
     ``outer`` counts separate planes of such rows inside a page (keys and values of several
     heads: ``(2, kv_heads)`` with ``inner = (head_dim,)``; one latent vector per token:
     ``()`` with ``inner = (width,)``).  ``window`` (None: every earlier token stays readable)
-    lets the cache manager take back the pages a trailing window has passed.  Runs whose
+    lets the cache manager take back the pages a trailing window has passed, except the pages
+    of a request's first ``keep_first`` tokens, which every later row still reads.  Runs whose
     needs are equal share a page pool and a block table."""
 
     outer: Tuple[int, ...] = ()
     inner: Tuple[int, ...] = ()
     dtype: Optional[torch.dtype] = None
     window: Optional[int] = None
+    keep_first: int = 0
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
         return (*self.outer, int(page_size), *self.inner)
@@ -222,6 +224,12 @@ class Norm(Part):
     rows are produced and ``x`` is left untouched."""
 
     def forward(self, x, out, delta=None, rows=None) -> None:
+        raise NotImplementedError
+
+    def add_normed(self, x, delta, mult: float, copy=None) -> None:
+        """For blocks that norm a sublayer's output instead of its input: add ``mult`` times the
+        normalised ``delta`` (32-bit partial sums) into the residual ``x``; ``copy`` (optional)
+        receives the updated rows in its own type."""
         raise NotImplementedError
 
 

@@ -89,3 +89,61 @@ class PreNormBlock(Block):
             return delta
         self.feed_forward_norm.forward(x, h, delta=delta)
         return self.feed_forward.forward(h, step)
+
+
+@register("block", "output_norm")
+class OutputNormBlock(Block):
+    """A layer whose norms act on what its sublayers PRODUCE, not on what they read:
+
+    ``x <- x + m * norm1(mixer(x))``, then ``x <- x + m * norm2(feed_forward(x))``
+
+    with one number ``m`` (``residual_mult``) for the whole layer.  Both sublayers read the
+    residual stream itself (rounded to the activation type in bfloat16, as it is in 32-bit).  The
+    norm, the scaling and the addition are one kernel, which also leaves the updated stream's copy
+    in the activation type for the sublayer that reads it next; nothing is left pending for the
+    block that follows.
+
+    Parameters: ``hidden_size``, ``mixer``, ``feed_forward`` (None: the mixer alone), ``mixer_norm``,
+    ``feed_forward_norm``, ``residual_mult`` (1.0) and the weight-name prefixes of :class:`PreNormBlock`."""
+
+    def __init__(self, params, env: BuildEnv):
+        super().__init__(params, env)
+        self.require("hidden_size", "mixer", "mixer_norm")
+        self.hidden = int(params["hidden_size"])
+        self.mult = float(params.get("residual_mult", 1.0))
+        self.mixer = build("mixer", params["mixer"], env)
+        self.mixer_norm = build("norm", params["mixer_norm"], env)
+        self._prefixes = {
+            params.get("mixer_prefix", "mixer."): self.mixer,
+            params.get("mixer_norm_prefix", "mixer_norm."): self.mixer_norm,
+        }
+        self.feed_forward = self.feed_forward_norm = None
+        if params.get("feed_forward") is not None:
+            self.require("feed_forward_norm")
+            self.feed_forward = build("feed_forward", params["feed_forward"], env)
+            self.feed_forward_norm = build("norm", params["feed_forward_norm"], env)
+            self._prefixes[params.get("feed_forward_prefix", "feed_forward.")] = self.feed_forward
+            self._prefixes[params.get("feed_forward_norm_prefix", "feed_forward_norm.")] = self.feed_forward_norm
+
+    def sub_parts(self) -> Dict[str, Part]:
+        return dict(self._prefixes)
+
+    def forward(self, x: torch.Tensor, delta, step, cache: LayerCache):
+        T = x.shape[0]
+        if delta is not None and not isinstance(delta, Deferred):
+            ops.residual_add(x, delta)           # what a block of another arrangement left pending
+        if self.env.dtype == torch.float32:
+            h = copy = None                      # the sublayers read the stream itself
+        else:
+            # the stream's copy in the activation type: left by the block before where that is one of this
+            # kind (it was the last thing written into the buffer), else made now
+            h = copy = self.env.workspace.get("block.stream_copy", (T, self.hidden), self.env.dtype)
+            if step.shared.get("block.stream_copy") is not x:
+                self.mixer_norm.add_normed(x, None, self.mult, copy)
+        delta = self.mixer.forward(x if h is None else h, step, cache)
+        self.mixer_norm.add_normed(x, delta, self.mult, copy)
+        if self.feed_forward is not None:
+            delta = self.feed_forward.forward(x if h is None else h, step)
+            self.feed_forward_norm.add_normed(x, delta, self.mult, copy)
+        step.shared["block.stream_copy"] = x     # the copy is up to date with this residual
+        return None

@@ -51,3 +51,8 @@ class RMSNorm(Norm):
 
     def forward(self, x, out, delta=None, rows=None) -> None:
         ops.add_rmsnorm(x, self._kernel_weight, self.eps, out, delta=delta, rows=rows)
+
+    def add_normed(self, x, delta, mult: float, copy=None) -> None:
+        """The norm on a sublayer's output: ``x += mult * norm(delta)``; ``copy`` (optional) receives
+        the updated rows in its own type."""
+        ops.norm_residual(x, delta, self.weight, self.eps, mult, copy)

@@ -12,6 +12,14 @@ model.rs:181-274).  With ``factor f``, ``low_freq_factor lo``, ``high_freq_facto
 ``n0/hi`` keeps its frequency, above ``n0/lo`` it is divided by ``f``, and in between the two
 are blended with weight ``s = (n0/wavelength - lo) / (hi - lo)``.
 
+The ``yarn`` scaling stretches only the slow pairs.  With ``factor s``, trained length
+``original n0`` and the turn counts ``fast`` and ``slow``: the pair that makes ``t`` turns over
+``n0`` positions has the real-valued index ``d(t) = dims ln(n0 / (2 pi t)) / (2 ln theta)``; with
+``lo = max(floor(d(fast)), 0)``, ``hi = min(ceil(d(slow)), dims - 1)`` and
+``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` pair ``i`` turns by
+``freq_i / s * ramp_i + freq_i * (1 - ramp_i)``, and cosine and sine are multiplied by
+``0.1 ln s + 1`` (``magnitude``).
+
 The table of frequencies is computed once in float64 and kept in float32; the angle is a
 32-bit product, and its cosine and sine are computed once per step for all layers.
 """
@@ -28,10 +36,37 @@ from .base import BuildEnv, PartError, PositionEncoding, register
 PAIRING = {"half": 0, "adjacent": 1}
 
 
+YARN_MAGNITUDE_SLOPE = 0.1      # cosine and sine grow by 0.1 ln(factor) + 1
+
+
+def yarn_ramp(head_dim: int, theta: float, scaling: Mapping) -> list:
+    """The weight of the stretched frequency for every pair (0: the pair keeps its frequency)."""
+    n0 = float(scaling["original"])
+
+    def index_of(turns: float) -> float:
+        return head_dim * math.log(n0 / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+    lo = max(math.floor(index_of(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(index_of(float(scaling["slow"]))), head_dim - 1)
+    return [min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0) for i in range(head_dim // 2)]
+
+
+def magnitude(scaling: Optional[Mapping]) -> float:
+    """The factor on cosine and sine (1 but for ``yarn``)."""
+    if scaling is not None and scaling.get("rope_type") == "yarn":
+        return YARN_MAGNITUDE_SLOPE * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
+
+
 def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[Mapping]) -> torch.Tensor:
     """float64 ``[head_dim/2]`` rotation frequencies after scaling."""
     half = head_dim // 2
     freqs = []
+    if scaling is not None and scaling.get("rope_type") == "yarn":
+        factor = float(scaling["factor"])
+        for i, ramp in enumerate(yarn_ramp(head_dim, theta, scaling)):
+            f = float(theta) ** (-(i / half))
+            freqs.append(f / factor * ramp + f * (1.0 - ramp))
+        return torch.tensor(freqs, dtype=torch.float64)
     for i in range(half):
         f = float(theta) ** (-(i / half))
         if scaling is not None:
@@ -51,8 +86,9 @@ def inverse_frequencies(head_dim: int, theta: float, scaling: Optional[Mapping])
 
 @register("position", "rope")
 class RotaryEmbedding(PositionEncoding):
-    """Parameters: ``head_dim``, ``theta``, ``scaling`` (mapping or None), ``pairing``
-    (``"half"`` or ``"adjacent"``)."""
+    """Parameters: ``head_dim`` (the number of rotated dimensions), ``theta``, ``scaling`` (mapping
+    or None; its ``rope_type`` is ``"llama3"`` (default) or ``"yarn"``), ``pairing`` (``"half"`` or
+    ``"adjacent"``)."""
 
     def __init__(self, params, env: BuildEnv):
         super().__init__(params, env)
@@ -65,8 +101,9 @@ class RotaryEmbedding(PositionEncoding):
             raise PartError(f"unknown rotary pairing {pairing!r} (known: {', '.join(PAIRING)})")
         self.pairing = PAIRING[pairing]
         scaling = params.get("scaling")
-        if scaling is not None and scaling.get("rope_type", "llama3") != "llama3":
+        if scaling is not None and scaling.get("rope_type", "llama3") not in ("llama3", "yarn"):
             raise PartError(f"unknown rope scaling {scaling.get('rope_type')!r}")
+        self.magnitude = magnitude(scaling)
         self.inv_freq = inverse_frequencies(self.head_dim, float(params["theta"]), scaling) \
             .to(torch.float32).to(env.device)
 
@@ -81,6 +118,6 @@ class RotaryEmbedding(PositionEncoding):
             T = step.num_tokens
             table = self.env.workspace.get(f"rope.table.{len(step.shared)}",
                                            (T, self.head_dim // 2, 2), torch.float32)
-            ops.rope_table(step.positions, self.inv_freq, table)
+            ops.rope_table(step.positions, self.inv_freq, table, self.magnitude)
             step.shared[self._key] = table
         return table, self.pairing
