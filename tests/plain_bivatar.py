@@ -75,23 +75,34 @@ def latent_keys(h, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float):
     return latent, shared
 
 
+def latent_attention(q, q_rot, latent, shared, uk, uv, scale: float) -> torch.Tensor:
+    """q [T, H, D] unrotated and q_rot [T, H, rot] rotated query parts, latent [S, R] and shared [S, rot]
+    of the S >= T tokens so far (the queries are the last T), uk [H*D, R], uv [H*E, R] -> [T, H, E].
+    Keys and values are formed per head, as the design writes them."""
+    T, H, D = q.shape
+    S = latent.shape[0]
+    E = uv.shape[0] // H
+    k = (latent @ uk.T).view(S, H, D)
+    v = (latent @ uv.T).view(S, H, E)
+    out = torch.zeros(T, H, E, dtype=q.dtype)
+    for t in range(T):
+        i = S - T + t
+        for a in range(H):
+            s = (k[:i + 1, a] @ q[t, a] + shared[:i + 1] @ q_rot[t, a]) * scale
+            out[t, a] = torch.softmax(s, dim=0) @ v[:i + 1, a]
+    return out
+
+
 def latent_attention_mixer(h, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float, kept) -> torch.Tensor:
     """``kept``: (latent, shared rotated key part) of this layer or of the layer it reads them from."""
     T = h.shape[0]
-    H, D, rot, E, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    H, D, rot, E = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
     latent, shared = kept
     q = (rms_norm(h @ w[p + "dq"].T, w[p + "dq.norm"], eps) @ w[p + "uq"].T).view(T, H, D + rot)
     freq, grow = stretched_frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"))
     q_rot = rotate_pairs(q[..., D:], torch.arange(T), freq, grow)
-    k = (latent @ w[p + "uk"].T).view(T, H, D)
-    v = (latent @ w[p + "uv"].T).view(T, H, E)
-    gate = torch.sigmoid(h @ w[p + "g"].T)                                  # [T, H]
-    out = torch.zeros(T, H, E, dtype=h.dtype)
-    for i in range(T):
-        for a in range(H):
-            s = (k[:i + 1, a] @ q[i, a, :D] + shared[:i + 1] @ q_rot[i, a]) * m["scale"]
-            out[i, a] = torch.softmax(s, dim=0) @ v[:i + 1, a]
-    out = out * gate[:, :, None]
+    out = latent_attention(q[..., :D], q_rot, latent, shared, w[p + "uk"], w[p + "uv"], m["scale"])
+    out = out * torch.sigmoid(h @ w[p + "g"].T)[:, :, None]
     return out.reshape(T, H * E) @ w[p + "o"].T
 
 
@@ -104,26 +115,32 @@ def visible(i: int, j: int, window: Optional[int], keep_first: int) -> bool:
     return j <= i and (window is None or i - j < window or j < keep_first)
 
 
+def sloped_window_attention(q, k, v, scale: float, window: Optional[int], keep_first: int) -> torch.Tensor:
+    """q [T, H, D], k [T, G, D], v [T, G, E] -> [T, H, E]; one query row at a time over the keys it sees."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    slopes = head_slopes(H)
+    out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
+    for i in range(T):
+        js = [j for j in range(i + 1) if visible(i, j, window, keep_first)]
+        idx = torch.tensor(js)
+        dist = torch.tensor([float(i - j) for j in js], dtype=q.dtype)
+        for a in range(H):
+            g = a // (H // G)
+            s = (k[idx, g] @ q[i, a]) * scale - slopes[a] * dist
+            out[i, a] = torch.softmax(s, dim=0) @ v[idx, g]
+    return out
+
+
 def window_attention_mixer(h, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> torch.Tensor:
     T = h.shape[0]
     H, G, D, E = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     mask = m.get("mask") or {}
-    window, keep_first = mask.get("size"), int(mask.get("keep_first") or 0)
     q = rms_norm((h @ w[p + "q"].T).view(T, H, D), w[p + "q.norm"], eps)
     k = rms_norm((h @ w[p + "k"].T).view(T, G, D), w[p + "k.norm"], eps)
     v = (h @ w[p + "v"].T).view(T, G, E)
-    gate = torch.sigmoid(h @ w[p + "g"].T)
-    slopes = head_slopes(H)
-    out = torch.zeros(T, H, E, dtype=h.dtype)
-    for i in range(T):
-        js = [j for j in range(i + 1) if visible(i, j, window, keep_first)]
-        idx = torch.tensor(js)
-        dist = torch.tensor([float(i - j) for j in js], dtype=h.dtype)
-        for a in range(H):
-            g = a // (H // G)
-            s = (k[idx, g] @ q[i, a]) * m["scale"] - slopes[a] * dist
-            out[i, a] = torch.softmax(s, dim=0) @ v[idx, g]
-    out = out * gate[:, :, None]
+    out = sloped_window_attention(q, k, v, m["scale"], mask.get("size"), int(mask.get("keep_first") or 0))
+    out = out * torch.sigmoid(h @ w[p + "g"].T)[:, :, None]
     return out.reshape(T, H * E) @ w[p + "o"].T
 
 
@@ -180,9 +197,11 @@ def tensor_shapes(config: dict) -> Dict[str, tuple]:
     return out
 
 
-def random_tensors(config: dict, seed: int) -> Dict[str, torch.Tensor]:
+def random_tensors(config: dict, seed: int, spread: float = 2.0) -> Dict[str, torch.Tensor]:
     """Random tensors (float64, every value a bfloat16 number): matrices with a spread of
-    ``2 / sqrt(in)`` so that scores and gates move, norm weights around one."""
+    ``spread / sqrt(in)``, norm weights around one.  With a spread of 2 scores and gates move far and the
+    softmax is sharp, which shows a wrong key at once but also carries rounding a long way; the bfloat16
+    tests take a spread of 1."""
     gen = torch.Generator().manual_seed(seed)
     out = {}
     for name, shape in tensor_shapes(config).items():
@@ -191,6 +210,16 @@ def random_tensors(config: dict, seed: int) -> Dict[str, torch.Tensor]:
         elif name == "embed":
             t = torch.randn(shape, generator=gen, dtype=torch.float64)
         else:
-            t = torch.randn(shape, generator=gen, dtype=torch.float64) * (2.0 / math.sqrt(shape[1]))
+            t = torch.randn(shape, generator=gen, dtype=torch.float64) * (spread / math.sqrt(shape[1]))
         out[name] = t.to(torch.bfloat16).to(torch.float64)
+    return out
+
+
+def greedy(config: dict, weights: Dict[str, torch.Tensor], prompt: Sequence[int], n: int) -> List[int]:
+    """``n`` tokens chosen by the largest logit, the whole sequence recomputed for each."""
+    toks, out = list(prompt), []
+    for _ in range(n):
+        t = int(torch.argmax(forward(config, weights, toks)[-1]))
+        out.append(t)
+        toks.append(t)
     return out
