@@ -1,7 +1,7 @@
 """Prefill and decode throughput of one design beside the dense Llama decoder of equal size,
 with the time of every kind of kernel in a step:
 
-    python bench.py --design viresun [--design-size small|base|wide]
+    python bench.py --design viresun|bivatar [--design-size small|base|wide]
 
 Both models have random bfloat16 weights drawn on the device, the same width, heads, head size,
 feed-forward size, number of layers and vocabulary.  Timed on the device with CUDA events after
@@ -39,6 +39,39 @@ def viresun_config(size: str) -> dict:
     return {"architecture": "Viresun", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6},
             "layers": [{"type": "attention", "mixer": attn, "mlp": dense}, {"type": "attention", "mixer": attn, "mlp": moe},
                        {"type": "mamba2", "mixer": mamba, "mlp": dense}, {"type": "attention", "mixer": attn, "mlp": moe}]}
+
+
+# name: (latent rank of keys and values, of queries, unrotated and rotated dimensions per head, value size,
+#        kept first tokens of the windowed layers); widths, heads, feed-forward and window as above
+LATENT_SIZES = {"small": (256, 512, 64, 32, 64, 16), "base": (512, 768, 128, 64, 128, 64),
+                "wide": (512, 1536, 128, 64, 128, 64)}
+
+
+def bivatar_config(size: str) -> dict:
+    """Four layers: attention through a latent, windowed attention that keeps first tokens, a latent layer of its
+    own, and one that reads the third layer's latent; all with the dense feed-forward."""
+    W, H, G, D, ff = SIZES[size][:5]
+    window = SIZES[size][8]
+    R, Q, nope, rot, E, keep = LATENT_SIZES[size]
+    rotation = {"dims": rot, "base": 10000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    latent = {"heads": H, "dim": nope, "rot_dim": rot, "vdim": E, "kv_rank": R, "q_rank": Q,
+              "scale": (nope + rot) ** -0.5, "rot": rotation}
+    attn = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5,
+            "mask": {"size": window, "keep_first": keep}}
+    dense = {"kind": "dense", "ff": ff}
+    return {"architecture": "Bivatar", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "embedding": {"scale": 1.0},
+            "layers": [{"type": "latent_attention", "mixer": latent, "mlp": dense},
+                       {"type": "attention", "mixer": attn, "mlp": dense},
+                       {"type": "latent_attention", "mixer": latent, "mlp": dense},
+                       {"type": "latent_attention", "mixer": dict(latent, kv_from=2), "mlp": dense}]}
+
+
+DESIGNS = {
+    "viresun": (viresun_config, "attention+dense, attention+routed, mamba2+dense, attention+routed"),
+    "bivatar": (bivatar_config, "latent attention, windowed attention with kept first tokens, latent attention, "
+                                "latent attention on the third layer's latent; dense feed-forwards"),
+}
 
 
 def llama_config(size: str) -> dict:
@@ -89,7 +122,7 @@ class DesignBench:
                        max_seqs=batch)
         self.cfg, model = random_model_on_device(raw, seed, env)
         for block in model.blocks:                       # a distance bias a trained model could have
-            if getattr(block.mixer, "r1", None) is not None:
+            if getattr(block.mixer, "r1", None) is not None and getattr(block.mixer, "r2", None) is not None:
                 block.mixer.r1.fill_(1.0)
                 block.mixer.r2.fill_(0.25)
         self.runner = ModelRunner(None, engine, model=model, model_config=self.cfg)
@@ -165,20 +198,24 @@ class DesignBench:
 
 def run(design: str, size: str, steps: int, warmup: int, batch: int, context: int, prefill: int, peaks: dict,
         sampler) -> dict:
-    if design != "viresun":
-        raise SystemExit(f"bench.py: no design named {design!r} (known: viresun)")
+    if design not in DESIGNS:
+        raise SystemExit(f"bench.py: no design named {design!r} (known: {', '.join(sorted(DESIGNS))})")
     from allpaca_b200 import ops
     from allpaca_b200.ops import library
-    out = {"metric": f"decode tok/s (viresun {size}, bf16)", "unit": "tok/s", "n_gpus": 1, "steps": steps,
+    make_config, layers = DESIGNS[design]
+    sizes = dict(zip(("width", "heads", "kv_heads", "head_dim", "ff", "experts", "top", "expert_ff", "window",
+                      "mamba_heads", "mamba_vdim", "state"), SIZES[size]))
+    if design == "bivatar":
+        sizes = {k: v for k, v in sizes.items() if k in ("width", "heads", "kv_heads", "head_dim", "ff", "window")}
+        sizes.update(zip(("kv_rank", "q_rank", "dim", "rot_dim", "vdim", "keep_first"), LATENT_SIZES[size]))
+    out = {"metric": f"decode tok/s ({design} {size}, bf16)", "unit": "tok/s", "n_gpus": 1, "steps": steps,
            "warmup": warmup, "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-           "config": {"design": "viresun", "size": size, "global_batch": batch, "seq_len": context,
-                      "prefill_tokens": prefill, "sizes": dict(zip(
-                          ("width", "heads", "kv_heads", "head_dim", "ff", "experts", "top", "expert_ff", "window",
-                           "mamba_heads", "mamba_vdim", "state"), SIZES[size])),
-                      "layers": "attention+dense, attention+routed, mamba2+dense, attention+routed; beside 4 Llama layers",
+           "config": {"design": design, "size": size, "global_batch": batch, "seq_len": context,
+                      "prefill_tokens": prefill, "sizes": sizes,
+                      "layers": layers + "; beside 4 Llama layers",
                       "weights": "random N(0,0.02)", "peaks": peaks["source"]}}
     sampler.start()
-    for name, raw in (("viresun", viresun_config(size)), ("llama", llama_config(size))):
+    for name, raw in ((design, make_config(size)), ("llama", llama_config(size))):
         t0 = time.time()
         wb = DesignBench(raw, context, prefill, batch)
         print(f"[bench] {name} {size} ready in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
@@ -194,7 +231,7 @@ def run(design: str, size: str, steps: int, warmup: int, batch: int, context: in
                      "prefill_median_ms": round(median, 3),
                      "prefill_kernels_ms": {k: round(v, 4) for k, v in sorted(ptab.items(), key=lambda kv: -kv[1])},
                      "decode_kernels_ms": {k: round(v, 4) for k, v in sorted(dtab.items(), key=lambda kv: -kv[1])}}
-        if name == "viresun":
+        if name == design:
             out["value"], out["ms_per_step"], out["gpu_launches"] = out[name]["decode_tok_s"], round(dms, 4), launches
         ops.check_kernel_status()
         wb.close()

@@ -15,7 +15,15 @@
 //                    and the shared key part rotated, both written into the row's page and slot
 //   head_project   : out[t, h, :N] = in[t, h, :K] W[h] for W [H, K, N]; the `tail` numbers behind
 //                    in[t, h, :K] are rotated by the row's position and put behind out[t, h, :N]
-//                    (queries into the latent space with their rotated part; latent outputs to values)
+//                    (queries into the latent space with their rotated part; latent outputs to values);
+//                    without W the K numbers are copied (queries rotated, nothing else)
+//   latent_gather  : the records of every token of the sequences that bring several rows, out of their
+//                    pages into one matrix in sequence order, with a table that says where each
+//                    sequence's token j went.  A long prompt is cheaper the other way round: one
+//                    product turns that matrix into per-head keys and values [token][head][k | k_rot | v]
+//                    (what a page of ONE token with H key/value heads looks like to the attention
+//                    kernels, the table being its block table), and the attention runs on the heads'
+//                    own small sizes.
 //
 // Norm statistics, angles and every sum are 32-bit.
 #include "common.cuh"
@@ -136,12 +144,17 @@ head_project_kernel(const TI* __restrict__ in, long long in_ld, int in_hs, const
         float acc[HP_ROWS];
 #pragma unroll
         for (int r = 0; r < HP_ROWS; ++r) acc[r] = 0.f;
-        const TW* wc = w + (size_t)h * K * N + n;
-#pragma unroll 4
-        for (int k = 0; k < K; ++k) {
-            const float wv = ap_to_float(wc[(size_t)k * N]);
+        if (w == nullptr) {                                  // no matrix: the numbers pass as they are
 #pragma unroll
-            for (int r = 0; r < HP_ROWS; ++r) acc[r] = fmaf(in_s[r * K + k], wv, acc[r]);
+            for (int r = 0; r < HP_ROWS; ++r) acc[r] = in_s[r * K + n];
+        } else {
+            const TW* wc = w + (size_t)h * K * N + n;
+#pragma unroll 4
+            for (int k = 0; k < K; ++k) {
+                const float wv = ap_to_float(wc[(size_t)k * N]);
+#pragma unroll
+                for (int r = 0; r < HP_ROWS; ++r) acc[r] = fmaf(in_s[r * K + k], wv, acc[r]);
+            }
         }
 #pragma unroll
         for (int r = 0; r < HP_ROWS; ++r)
@@ -160,6 +173,7 @@ AP_EXPORT int ap_head_project(const void* in, int in_dtype, long long in_ld, int
                               void* out, int out_dtype, long long out_ld, int out_hs, int T, int H, int K, int N,
                               int tail, int tail_dims, const float* cos_sin, cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && H > 0 && K > 0 && N > 0 && tail >= 0, "head_project: bad sizes T=%d H=%d K=%d N=%d", T, H, K, N);
+    AP_REQUIRE(w != nullptr || N == K, "head_project: without a matrix the numbers are copied, N must equal K");
     AP_REQUIRE(H <= 65535, "head_project: %d heads exceed the grid", H);
     AP_REQUIRE(in_hs >= K + tail && out_hs >= N + tail && in_ld >= (long long)H * in_hs && out_ld >= (long long)H * out_hs,
                "head_project: the strides do not hold the heads");
@@ -185,6 +199,55 @@ AP_EXPORT int ap_head_project(const void* in, int in_dtype, long long in_ld, int
     else if (in_dtype == AP_F32 && w_dtype == AP_BF16 && out_dtype == AP_BF16) LAUNCH(float, bf16, bf16);
     else if (in_dtype == AP_BF16 && w_dtype == AP_BF16 && out_dtype == AP_BF16) LAUNCH(bf16, bf16, bf16);
     else AP_REQUIRE(false, "head_project: unsupported dtypes in=%d w=%d out=%d", in_dtype, w_dtype, out_dtype);
+#undef LAUNCH
+    return AP_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// One CTA per gathered token.  Sequences that bring one row are left out (their attention runs in
+// the latent space); the others' tokens 0 .. context-1 follow one another in sequence order.
+// where[s, j] is the row of `out` that holds token j of sequence s.
+// ---------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void latent_gather_kernel(const TA* __restrict__ cache, size_t page_stride, int P, int RS,
+                                     const int* __restrict__ block_table, int max_blocks,
+                                     const int* __restrict__ seq_start, const int* __restrict__ context_lens, int nseq,
+                                     TA* __restrict__ out, int* __restrict__ where, int width) {
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    int b = blockIdx.x, seq = -1;
+    for (int s = 0; s < nseq; ++s) {
+        const int n = (seq_start[s + 1] - seq_start[s] > 1) ? context_lens[s] : 0;
+        if (b < n) {
+            seq = s;
+            break;
+        }
+        b -= n;
+    }
+    if (seq < 0) return;
+    const int page = block_table[(size_t)seq * max_blocks + b / P];
+    const TA* src = cache + (size_t)page * page_stride + (size_t)(b % P) * RS;
+    TA* dst = out + (size_t)blockIdx.x * RS;
+    for (int d = threadIdx.x; d < RS; d += blockDim.x) dst[d] = src[d];
+    if (threadIdx.x == 0) where[(size_t)seq * width + b] = blockIdx.x;
+}
+
+AP_EXPORT int ap_latent_gather(const void* cache, int dtype, long long page_stride, int P, int RS,
+                               const int* block_table, int max_blocks, const int* seq_start, const int* context_lens,
+                               int nseq, void* out, int* where, int width, int total, cudaStream_t stream) {
+    AP_REQUIRE(P > 0 && RS > 0 && max_blocks > 0 && nseq >= 0 && width > 0 && total >= 0,
+               "latent_gather: bad sizes page=%d record=%d sequences=%d", P, RS, nseq);
+    AP_REQUIRE(cache && block_table && seq_start && context_lens && out && where, "latent_gather: a pointer is missing");
+    if (total == 0 || nseq == 0) return AP_OK;
+    const int threads = RS >= 256 ? 256 : (RS >= 128 ? 128 : 64);
+#define LAUNCH(TA)                                                                                                     \
+    AP_CHECK_PDL_LAUNCH("latent_gather",                                                                               \
+                        ap_launch_pdl(latent_gather_kernel<TA>, dim3((unsigned)total), dim3(threads), 0, stream,       \
+                                      (const TA*)cache, (size_t)page_stride, P, RS, block_table, max_blocks, seq_start, \
+                                      context_lens, nseq, (TA*)out, where, width))
+    if (dtype == AP_F32) LAUNCH(float);
+    else if (dtype == AP_BF16) LAUNCH(bf16);
+    else AP_REQUIRE(false, "latent_gather: unknown dtype %d", dtype);
 #undef LAUNCH
     return AP_OK;
 }

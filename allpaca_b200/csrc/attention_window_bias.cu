@@ -308,9 +308,11 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
                                  size_t page_stride, float scale, int window, const float* __restrict__ r1,
                                  const float* __restrict__ r2, int skip_single, int RS, int voff, int bias_kind,
                                  int keep_first, const float* __restrict__ gate, long long gate_ld) {
+    // the widest keys leave room for a shorter table (48 KB of static shared memory in all)
+    constexpr int BIAS_TABLE = DK > 128 ? MMA_BIAS_TABLE / 2 : MMA_BIAS_TABLE;
     __shared__ __align__(16) bf16 k_s[MK][DK + 8];
     __shared__ __align__(16) bf16 vt_s[DV][MK + 8];
-    __shared__ float bias_s[MMA_BIAS_TABLE];               // r1 ln(1 + r2 d) for the distances this CTA meets
+    __shared__ float bias_s[BIAS_TABLE];                   // r1 ln(1 + r2 d) for the distances this CTA meets
     ap_pdl_trigger();
     ap_pdl_wait();
     int b = blockIdx.x, seq = -1, row0 = 0, nrows = 0;
@@ -353,7 +355,7 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
     const int klo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
     // the largest distance any row of this CTA has to a key it may see
     const int span = pos_last - klo + 1;
-    const bool tabled = bias_kind == BIAS_LOG && span <= MMA_BIAS_TABLE;
+    const bool tabled = bias_kind == BIAS_LOG && span <= BIAS_TABLE;
     if (tabled)
         for (int d = threadIdx.x; d < span; d += AWB_THREADS) bias_s[d] = b1h * log1pf(b2h * (float)d);
     const int kfe = keep_first < klo ? keep_first : klo;       // kept first tokens before the first row's window
@@ -710,15 +712,16 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
     if (bias_kind == BIAS_NONE) r1 = r2 = nullptr;
     if (T == 0 || nseq == 0) return AP_OK;
     const bool wide = VD > MAX_HEAD;                      // more value columns per lane: the kernels built for NC = 20
-    // single_rows: sequences that bring one row go to the kernel made for them; other_rows: there are
-    // sequences with another number of rows (both 0: everything on the general kernel)
+    // single_rows 1: sequences that bring one row go to the kernel made for them; 2: they are left out (the
+    // caller serves them otherwise); other_rows: there are sequences with another number of rows (both 0:
+    // everything on the general kernel)
     // the decode kernel keeps a tile of value rows per warp in shared memory: where the values are too wide
     // for that, sequences of one row run on the general kernel like the others
-    if (single_rows && (size_t)DEC_WARPS * KT * ((VD + 7) / 8 * 8 + 8) * (dtype == AP_F32 ? 4 : 2) > 160 * 1024) {
+    if (single_rows == 1 && (size_t)DEC_WARPS * KT * ((VD + 7) / 8 * 8 + 8) * (dtype == AP_F32 ? 4 : 2) > 160 * 1024) {
         single_rows = 0;
         other_rows = 1;
     }
-    if (single_rows) {
+    if (single_rows == 1) {
         const int rep = nh / nkv;
         // all query heads of a key/value head in one CTA (every key read once) where that still fills the
         // GPU; else fewer heads per CTA and the keys read again from L2
@@ -755,9 +758,9 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         if (!other_rows) return AP_OK;
     }
     const int skip_single = single_rows ? 1 : 0;
-    if (dtype == AP_BF16 && D <= 128 && VD <= 128) {
-        // the tensor-core kernel, built for head sizes rounded up to 32, 64 or 128
-        const int dk = D <= 32 ? 32 : (D <= 64 ? 64 : 128), dv = VD <= 32 ? 32 : (VD <= 64 ? 64 : 128);
+    if (dtype == AP_BF16 && D <= 192 && VD <= 128) {
+        // the tensor-core kernel, built for head sizes rounded up to 32, 64, 128 (keys also 192)
+        const int dk = D <= 32 ? 32 : (D <= 64 ? 64 : (D <= 128 ? 128 : 192)), dv = VD <= 32 ? 32 : (VD <= 64 ? 64 : 128);
 #define MMA_ARGS q, out, cache, block_table, max_blocks, seq_start, positions, nseq, T, nh, nkv, D, VD, P, page_stride, \
                  scale, window, r1, r2, skip_single, RS, voff, bias_kind, keep_first, gate, gate_ld, stream
         switch (dk * 1000 + dv) {
@@ -769,6 +772,9 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
             case 64128: return launch_awb_mma<64, 128>(MMA_ARGS);
             case 128032: return launch_awb_mma<128, 32>(MMA_ARGS);
             case 128064: return launch_awb_mma<128, 64>(MMA_ARGS);
+            case 192032: return launch_awb_mma<192, 32>(MMA_ARGS);
+            case 192064: return launch_awb_mma<192, 64>(MMA_ARGS);
+            case 192128: return launch_awb_mma<192, 128>(MMA_ARGS);
             default: return launch_awb_mma<128, 128>(MMA_ARGS);
         }
 #undef MMA_ARGS

@@ -56,6 +56,9 @@ _CORE_SIGNATURES = {
     # int ap_head_project(in, in_dtype, in_ld, in_hs, w, w_dtype, out, out_dtype, out_ld, out_hs, T, H, K, N, tail,
     #                     tail_dims, cos_sin, stream)
     "ap_head_project": [_P, _I, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    # int ap_latent_gather(cache, dtype, page_stride, P, record, block_table, max_blocks, seq_start, context_lens,
+    #                      nseq, out, where, width, total, stream)
+    "ap_latent_gather": [_P, _I, _L, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _P],
     # int ap_causal_conv_silu(in, ld_in, col0, w, bias, state, state_stride, token_seq, seq_start, positions,
     #                         state_slots, out, T, nseq, C, taps, stream)
     "ap_causal_conv_silu": [_P, _L, _I, _P, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],

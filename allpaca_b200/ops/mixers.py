@@ -113,7 +113,8 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
     ``sigmoid(gate[t, h])``.  A token's record holds its key at 0 and its value at ``value_offset``
     (default: side by side, ``record = D + VD`` and ``value_offset = D``).
 
-    ``single_rows``: sequences that bring one row run on the kernel made for decoding (the query
+    ``single_rows``: ``"skip"``: sequences that bring one row are left out (the caller serves them
+    otherwise); True: sequences that bring one row run on the kernel made for decoding (the query
     heads of a key/value head together, the key tiles spread over the warps); ``other_rows`` says
     whether the step has sequences of another length as well (they run on the general kernel,
     which serves everything when ``single_rows`` is False)."""
@@ -151,7 +152,7 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
          block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(), positions.data_ptr(), int(num_seqs), T,
          num_heads, num_kv_heads, key_dim, value_dim, P, page_stride, float(scale), int(window or 0),
          r1.data_ptr() if r1 is not None else 0, r2.data_ptr() if r2 is not None else 0,
-         1 if single_rows else 0, 1 if other_rows else 0, record, value_offset, BIAS_KINDS[bias], int(keep_first or 0),
+         2 if single_rows == "skip" else (1 if single_rows else 0), 1 if other_rows else 0, record, value_offset, BIAS_KINDS[bias], int(keep_first or 0),
          gptr, gld, stream_handle())
 
 
@@ -201,17 +202,26 @@ def latent_prepare(proj: torch.Tensor, q_col: int, q_rank: int, q_weight: Option
          tsptr, btptr, maxb, P, page_stride, csptr, float(eps), T, stream_handle())
 
 
-def head_project(inp: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, heads: int, tail: int = 0,
+def head_project(inp: torch.Tensor, weight: Optional[torch.Tensor], out: torch.Tensor, heads: int, tail: int = 0,
                  tail_dims: int = 0, cos_sin: Optional[torch.Tensor] = None) -> None:
     """``out[t, h, :N] = inp[t, h, :K] @ weight[h]`` for ``weight [heads, K, N]``, every sum 32-bit in
     ascending ``k``.  ``inp [T, heads*(K + tail)]`` and ``out [T, heads*(N + tail)]``: the ``tail``
     numbers behind a head's ``K`` inputs go behind its ``N`` outputs, the first ``tail_dims`` of them
-    rotated by ``cos_sin [T, tail_dims/2, 2]`` (entry ``i`` paired with ``i + tail_dims/2``)."""
+    rotated by ``cos_sin [T, tail_dims/2, 2]`` (entry ``i`` paired with ``i + tail_dims/2``).  With
+    ``weight`` None the ``K`` numbers are copied (``out`` has ``inp``'s shape): a rotation alone."""
     _check(inp, "inp", dims=2)
-    _check(weight, "weight", dims=3)
     _check(out, "out", dims=2)
     T = inp.shape[0]
-    H, K, N = weight.shape
+    if weight is None:
+        H = heads
+        K = N = inp.shape[1] // H - tail
+        if K <= 0:
+            raise KernelError("head_project: without a matrix the rows must hold more than the tails")
+        weight_ptr, weight_code = 0, dtype_code(out.dtype)
+    else:
+        _check(weight, "weight", dims=3)
+        H, K, N = weight.shape
+        weight_ptr, weight_code = weight.data_ptr(), dtype_code(weight.dtype)
     if H != heads or inp.shape[1] != H * (K + tail) or tuple(out.shape) != (T, H * (N + tail)):
         raise KernelError(f"head_project: inp {tuple(inp.shape)}, weight {tuple(weight.shape)} and out "
                           f"{tuple(out.shape)} disagree (tail {tail})")
@@ -221,8 +231,8 @@ def head_project(inp: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, hea
         if tuple(cos_sin.shape) != (T, tail_dims // 2, 2):
             raise KernelError("head_project: cos_sin must be [T, tail_dims/2, 2]")
         csptr = cos_sin.data_ptr()
-    call(core(), "ap_head_project", inp.data_ptr(), dtype_code(inp.dtype), inp.stride(0), K + tail, weight.data_ptr(),
-         dtype_code(weight.dtype), out.data_ptr(), dtype_code(out.dtype), out.stride(0), N + tail, T, H, K, N,
+    call(core(), "ap_head_project", inp.data_ptr(), dtype_code(inp.dtype), inp.stride(0), K + tail, weight_ptr,
+         weight_code, out.data_ptr(), dtype_code(out.dtype), out.stride(0), N + tail, T, H, K, N,
          int(tail), int(tail_dims), csptr, stream_handle())
 
 
@@ -306,3 +316,24 @@ def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: Optional[torch
     call(core(), "ap_gated_group_rmsnorm", y.data_ptr(), z.data_ptr(), z.stride(0),
          weight.data_ptr() if weight is not None else 0, dtype_code(weight.dtype) if weight is not None else AP_F32,
          float(eps), out.data_ptr(), dtype_code(out.dtype), T, inner, int(parts), stream_handle())
+
+
+def latent_gather(cache_layer: torch.Tensor, block_table: torch.Tensor, seq_start: torch.Tensor,
+                  context_lens: torch.Tensor, num_seqs: int, out: torch.Tensor, where: torch.Tensor) -> None:
+    """The records of all tokens (0 to the last of this step) of every sequence that brings several
+    rows, from the pages ``cache_layer [pages, P, record]`` into the rows of ``out [total, record]`` in
+    sequence order; ``where [num_seqs, width]`` (int32) receives, for token ``j`` of sequence ``s``, its
+    row in ``out``.  ``total`` must be the sum of those sequences' context lengths."""
+    if cache_layer.dim() != 3 or not cache_layer.is_cuda or not cache_layer[0].is_contiguous():
+        raise KernelError("latent_gather: the pages must be [pages, P, record] with contiguous pages")
+    _check(out, "out", cache_layer.dtype, 2)
+    _check(where, "where", torch.int32, 2)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(seq_start, "seq_start", torch.int32, 1)
+    _check(context_lens, "context_lens", torch.int32, 1)
+    if out.shape[1] != cache_layer.shape[2] or where.shape[0] < num_seqs or seq_start.shape[0] < num_seqs + 1:
+        raise KernelError("latent_gather: shapes disagree")
+    call(core(), "ap_latent_gather", cache_layer.data_ptr(), dtype_code(cache_layer.dtype), cache_layer.stride(0),
+         cache_layer.shape[1], cache_layer.shape[2], block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(),
+         context_lens.data_ptr(), int(num_seqs), out.data_ptr(), where.data_ptr(), where.shape[1], out.shape[0],
+         stream_handle())

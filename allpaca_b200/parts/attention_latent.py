@@ -21,6 +21,14 @@ per-head keys and values: since ``q . (W_uk[a] c) = (W_uk[a]^T q) . c`` and
 ``sum_j p_j W_uv[a] c_j = W_uv[a] sum_j p_j c_j``, queries are carried into the latent space, the
 attention runs there with ONE key/value head whose value is the head of its key's record, and its
 result is carried out through ``W_uv``.  Norms, angles, scores, softmax, gate and all sums are 32-bit.
+
+That form reads little, which is what decoding wants, but a score costs ``kv_rank + rot_dim``
+multiplications instead of ``head_dim + rot_dim``.  Where the latent is wide (a record of more than 128
+numbers) the bfloat16 engine therefore serves sequences that bring several rows the other way round:
+the records of their tokens so far are gathered from the pages, ONE product with the matrix
+``[W_uk[a] | 0; 0 | I; W_uv[a] | 0]`` stacked over the heads turns them into per-head
+``[key | rotated key part | value]`` rows, and the tensor-core attention kernel runs on those (to it, pages
+of one token with ``H`` key/value heads).  The identity block copies the rotated part exactly.
 """
 from __future__ import annotations
 
@@ -75,6 +83,12 @@ class LatentAttention(Mixer):
         self.uq = Linear(env, self.nh * (self.hd + self.rot), self.Q)
         self.o = Linear(env, self.hidden, self.nh * self.vd)
         self.uk = self.uv = self.q_weight = self.kv_weight = None
+        # the per-head form for prompt portions (see the module's text): where the latent space is too wide for
+        # the tensor-core attention kernel and the heads' own sizes are not
+        rec = self.R + self.rot
+        self.expands = (env.dtype == torch.bfloat16 and rec > 128 and rec % 8 == 0
+                        and self.hd + self.rot <= 192 and self.vd <= 128)
+        self.expand = Linear(env, self.nh * (self.hd + self.rot + self.vd), rec) if self.expands else None
 
     def weights(self) -> Dict[str, WeightSpec]:
         w = {"dq": WeightSpec((self.Q, self.hidden)), "dq.norm": WeightSpec((self.Q,), "norm"),
@@ -99,6 +113,15 @@ class LatentAttention(Mixer):
         self.uk = tensors["uk"].view(self.nh, self.hd, self.R).contiguous()
         self.uv = tensors["uv"].view(self.nh, self.vd, self.R).transpose(1, 2).contiguous()
         self.q_weight = tensors["dq.norm"].float().contiguous()
+        if self.expands:
+            uk3 = tensors["uk"].view(self.nh, self.hd, self.R)
+            uv3 = tensors["uv"].view(self.nh, self.vd, self.R)
+            w = torch.zeros(self.nh, self.hd + self.rot + self.vd, self.R + self.rot, dtype=uk3.dtype, device=uk3.device)
+            w[:, :self.hd, :self.R] = uk3
+            w[:, self.hd:self.hd + self.rot, self.R:] = torch.eye(self.rot, dtype=uk3.dtype, device=uk3.device)
+            w[:, self.hd + self.rot:, :self.R] = uv3
+            self.expand.load(w.view(-1, self.R + self.rot))
+            self.expands = self.expand.uses_tensor_cores()
         if not self.shares_latent:
             self.kv_weight = tensors["dkv.norm"].float().contiguous()
 
@@ -120,16 +143,35 @@ class LatentAttention(Mixer):
                            table, cos_sin, self.eps)
         q = self.uq.forward(cq, "lattn.q", "float32")
         rec = self.R + self.rot
-        qa = ws.get("lattn.qa", (T, self.nh * rec), dt)
-        ops.head_project(q, self.uk, qa, self.nh, tail=self.rot, tail_dims=self.rot_dims, cos_sin=cos_sin)
         gate = proj[:, self.Q + self.kv_size:] if self.output_gate else None
-        ol = ws.get("lattn.ol", (T, self.nh * self.R), dt)
         lens = step.host_query_lens
-        single = dt == torch.bfloat16 and (step.max_query_len == 1 or 1 in lens)
-        ops.attention_window_bias(qa, ol, cache.pages, table, step.seq_start, step.positions, step.num_seqs,
-                                  self.nh, 1, rec, self.R, self.scale, 0, None, None, single_rows=single,
-                                  other_rows=step.max_query_len != 1, bias=None, gate=gate, record=rec,
-                                  value_offset=0)
+        singles = step.max_query_len == 1 or 1 in lens
+        per_head = self.expands and step.max_query_len > 1
         ov = ws.get("lattn.ov", (T, self.nh * self.vd), dt)
-        ops.head_project(ol, self.uv, ov, self.nh)
+        if singles or not per_head:
+            # in the latent space: every row, or (beside the per-head form) the sequences that bring one row
+            qa = ws.get("lattn.qa", (T, self.nh * rec), dt)
+            ops.head_project(q, self.uk, qa, self.nh, tail=self.rot, tail_dims=self.rot_dims, cos_sin=cos_sin)
+            ol = ws.get("lattn.ol", (T, self.nh * self.R), dt)
+            ops.attention_window_bias(qa, ol, cache.pages, table, step.seq_start, step.positions, step.num_seqs,
+                                      self.nh, 1, rec, self.R, self.scale, 0, None, None,
+                                      single_rows=dt == torch.bfloat16 and singles,
+                                      other_rows=step.max_query_len != 1 and not per_head, bias=None, gate=gate,
+                                      record=rec, value_offset=0)
+            ops.head_project(ol, self.uv, ov, self.nh)
+        if per_head:
+            # the sequences that bring several rows, on per-head keys and values of all their tokens so far
+            spans = [f + n for f, n in zip(step.host_first_position, lens) if n > 1]
+            total, width = sum(spans), max(spans)
+            gathered = ws.get("lattn.gathered", (total, rec), dt)
+            where = ws.get("lattn.where", (step.num_seqs, width), torch.int32)
+            ops.latent_gather(cache.pages, table, step.seq_start, step.context_lens, step.num_seqs, gathered, where)
+            kv = self.expand.forward(gathered, "lattn.expanded", "either")
+            key = self.hd + self.rot
+            qr = ws.get("lattn.qr", (T, self.nh * key), dt)
+            ops.head_project(q, None, qr, self.nh, tail=self.rot, tail_dims=self.rot_dims, cos_sin=cos_sin)
+            ops.attention_window_bias(qr, ov, kv.view(total, self.nh, 1, key + self.vd), where, step.seq_start,
+                                      step.positions, step.num_seqs, self.nh, self.nh, key, self.vd, self.scale, 0,
+                                      None, None, single_rows="skip" if singles else False, other_rows=True, bias=None,
+                                      gate=gate, record=key + self.vd, value_offset=key)
         return self.o.forward(ov, "lattn.o", "delta")

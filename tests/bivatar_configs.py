@@ -92,4 +92,15 @@ ONLY_WINDOW = {
     "layers": [layer("attention", window(2, 1, 16, 8, 0.25, size=9, keep_first=4), None),
                layer("attention", window(4, 4, 8, 8, 0.3), dense(48))],
 }
-CONFIGS = {"A": BIVATAR_A, "B": BIVATAR_B, "C": BIVATAR_C}
+# a latent wider than the tensor-core attention kernel takes (136 + 16): prompt portions in bfloat16 run on keys
+# and values formed per head, single rows in the latent space; a second layer reads the same latent
+BIVATAR_D = {
+    "architecture": "Bivatar", "vocab": 128, "width": 64, "norm": {"eps": 1e-5}, "residual_mult": 0.7,
+    "embedding": {"scale": 1.2},
+    "layers": [
+        layer("latent_attention", latent(3, 24, 16, 40, 136, 32, 0.17, ROT_A), dense(64)),
+        layer("attention", window(2, 1, 16, 24, 0.25, size=30, keep_first=9), None),
+        layer("latent_attention", latent(5, 40, 16, 8, 136, 48, 0.14, ROT_A, kv_from=0), dense(40)),
+    ],
+}
+CONFIGS = {"A": BIVATAR_A, "B": BIVATAR_B, "C": BIVATAR_C, "D": BIVATAR_D}

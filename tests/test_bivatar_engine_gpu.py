@@ -16,7 +16,7 @@ from bivatar_configs import CONFIGS, ONLY_LATENT, ONLY_WINDOW
 pytestmark = pytest.mark.gpu
 
 TOL = {"float32": 2e-5, "bfloat16": 3e-2}
-LENGTHS = {"A": [1, 2, 23, 61, 150], "B": [1, 3, 40, 97], "C": [1, 5, 50, 33]}
+LENGTHS = {"A": [1, 2, 23, 61, 150], "B": [1, 3, 40, 97], "C": [1, 5, 50, 33], "D": [1, 2, 70, 131]}
 
 
 def write_folder(path, config, seed, dtype):
@@ -66,8 +66,8 @@ def check(got, want, tol, what, tally=None):
         tally.over += int((err > tol).sum())
 
 
-@pytest.fixture(scope="module", params=[("A", "float32"), ("B", "float32"), ("C", "float32"), ("A", "bfloat16"),
-                                        ("B", "bfloat16"), ("C", "bfloat16")],
+@pytest.fixture(scope="module", params=[("A", "float32"), ("B", "float32"), ("C", "float32"), ("D", "float32"),
+                                        ("A", "bfloat16"), ("B", "bfloat16"), ("C", "bfloat16"), ("D", "bfloat16")],
                 ids=lambda p: f"{p[0]}-{p[1]}")
 def case(request, tmp_path_factory):
     name, dtype = request.param
