@@ -1,0 +1,305 @@
+// Decoding through a latent that all heads share: sequences that bring ONE row, bfloat16.
+//
+// A token's record [c | k_rot] (D numbers) is the key of every head, and its first R numbers are
+// every head's value (attention_latent.cu says why).  So the H query rows of a sequence meet the
+// same keys: a CTA takes 16 heads of one sequence and a slice of its keys, and every key tile that
+// reaches shared memory serves all 16 rows on the tensor cores (mma.sync m16n8k16, 32-bit sums):
+//
+//   S [16 heads x 64 keys] = Q [16 x D] K^T      warp w: keys 16w .. 16w+15 of the tile
+//   online softmax over the tile                  row maxima of the four warps meet in shared memory
+//   O [16 x R] += P [16 x 64] V [64 x R]          warp w: its quarter of the R columns; V is the same
+//                                                 tile, read transposed (ldmatrix.trans)
+//
+// Key tiles come by cp.async into two buffers, the next one loading while this one is used.  The
+// slices of a sequence's keys leave unnormalised sums with their maximum and weight sum; a second
+// kernel merges them, applies the output gate and rounds.  Scores, softmax and sums are 32-bit.
+#include "common.cuh"
+#include <float.h>
+
+#define LD_THREADS 128
+#define LD_KT 64              // keys per tile
+#define LD_M 16               // heads per CTA
+#define LD_PP 72              // row pitch of the probabilities in shared memory (64 + 8)
+
+__device__ __forceinline__ void ld_cp_async16(void* smem, const void* gmem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void ld_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void ld_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ld_ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s) : "memory");
+}
+__device__ __forceinline__ void ld_ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s) : "memory");
+}
+__device__ __forceinline__ void ld_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t ld_pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// NBW: blocks of 8 value columns per warp (R <= 32 NBW)
+template <int NBW>
+__global__ void __launch_bounds__(LD_THREADS)
+latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, const int* __restrict__ block_table,
+                     int max_blocks, const int* __restrict__ seq_start, const int* __restrict__ positions, int nh, int D,
+                     int R, int P, size_t page_stride, float scale, int nsplit, float* __restrict__ part_o,
+                     float* __restrict__ part_ml) {
+    extern __shared__ __align__(16) unsigned char ld_smem[];
+    const int seq = blockIdx.x, h0 = blockIdx.y * LD_M, split = blockIdx.z;
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    const int row = seq_start[seq];
+    if (seq_start[seq + 1] - row != 1) return;
+    const int qpos = positions[row];
+    const int D16 = (D + 15) & ~15;
+    const int pitch = D16 + 8;                               // 16 bytes more than a row: ldmatrix meets no bank twice
+    bf16* q_s = reinterpret_cast<bf16*>(ld_smem);            // [16][pitch]
+    bf16* k_s = q_s + LD_M * pitch;                          // [2][64][pitch]
+    bf16* p_s = k_s + 2 * LD_KT * pitch;                     // [16][LD_PP]
+    float* red = reinterpret_cast<float*>(p_s + LD_M * LD_PP);   // [4][16]
+    const int* table = block_table + (size_t)seq * max_blocks;
+    const int tiles = qpos / LD_KT + 1;
+    const int per = (tiles + nsplit - 1) / nsplit;
+    const int t0 = split * per, t1 = min(tiles, t0 + per);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+    const int chunks = D16 / 8;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < LD_M * chunks; i += LD_THREADS) {
+        const int r = i / chunks, c = (i - r * chunks) * 8;
+        uint4 v = zero;
+        if (h0 + r < nh && c < D) v = *reinterpret_cast<const uint4*>(q + ((size_t)row * nh + h0 + r) * D + c);
+        *reinterpret_cast<uint4*>(q_s + r * pitch + c) = v;
+    }
+    auto load_tile = [&](int tile, int stage) {
+        bf16* dst = k_s + (size_t)stage * LD_KT * pitch;
+        for (int i = threadIdx.x; i < LD_KT * chunks; i += LD_THREADS) {
+            const int j = i / chunks, c = (i - j * chunks) * 8;
+            const int kp = tile * LD_KT + j;
+            bf16* d = dst + j * pitch + c;
+            if (kp <= qpos && c < D)
+                ld_cp_async16(d, cache + (size_t)table[kp / P] * page_stride + (size_t)(kp % P) * D + c);
+            else
+                *reinterpret_cast<uint4*>(d) = zero;         // keys behind the row and the padding: finite, weight zero
+        }
+        ld_cp_async_commit();
+    };
+    float o[NBW][4];
+#pragma unroll
+    for (int i = 0; i < NBW; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-FLT_MAX, -FLT_MAX}, l[2] = {0.f, 0.f};
+    if (t0 < t1) load_tile(t0, 0);
+    for (int tile = t0; tile < t1; ++tile) {
+        const int stage = (tile - t0) & 1;
+        if (tile + 1 < t1) {
+            load_tile(tile + 1, stage ^ 1);
+            ld_cp_async_wait<1>();
+        } else {
+            ld_cp_async_wait<0>();
+        }
+        __syncthreads();                                     // the tile (and, the first time, the queries) are there
+        const bf16* kt = k_s + (size_t)stage * LD_KT * pitch;
+        float s[2][4];
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+        for (int ks = 0; ks < D16 / 16; ++ks) {
+            uint32_t a[4], b[4];
+            ld_ldsm_x4(a, q_s + (lane & 15) * pitch + ks * 16 + (lane >> 4) * 8);
+            ld_ldsm_x4(b, kt + (16 * warp + (lane & 7) + ((lane >> 4) & 1) * 8) * pitch + ks * 16 + ((lane >> 3) & 1) * 8);
+            ld_mma(s[0], a, b[0], b[1]);
+            ld_mma(s[1], a, b[2], b[3]);
+        }
+        float mx[2] = {-FLT_MAX, -FLT_MAX};
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int kp = tile * LD_KT + 16 * warp + nb * 8 + 2 * t4 + (e & 1);
+                const float v = kp <= qpos ? s[nb][e] * scale : -FLT_MAX;
+                s[nb][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+        }
+        if (t4 == 0) {
+            red[warp * LD_M + g] = mx[0];
+            red[warp * LD_M + g + 8] = mx[1];
+        }
+        __syncthreads();
+        float alpha[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = g + 8 * i;
+            const float mm = fmaxf(fmaxf(red[r], red[LD_M + r]), fmaxf(red[2 * LD_M + r], red[3 * LD_M + r]));
+            const float m_new = fmaxf(m[i], mm);
+            alpha[i] = __expf(m[i] - m_new);
+            m[i] = m_new;
+            l[i] *= alpha[i];
+        }
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                // the weight is rounded to bfloat16 for the second product: the fast exponential's error is far below that
+                const float p = s[nb][e] > -FLT_MAX ? __expf(s[nb][e] - m[e >> 1]) : 0.f;
+                s[nb][e] = p;
+                l[e >> 1] += p;
+            }
+            const int c = 16 * warp + nb * 8 + 2 * t4;
+            *reinterpret_cast<uint32_t*>(p_s + g * LD_PP + c) = ld_pack(s[nb][0], s[nb][1]);
+            *reinterpret_cast<uint32_t*>(p_s + (g + 8) * LD_PP + c) = ld_pack(s[nb][2], s[nb][3]);
+        }
+#pragma unroll
+        for (int i = 0; i < NBW; ++i) {
+            o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+            o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        }
+        __syncthreads();                                     // the probabilities of all 64 keys are written
+#pragma unroll
+        for (int kk = 0; kk < LD_KT / 16; ++kk) {
+            uint32_t a[4];
+            ld_ldsm_x4(a, p_s + (lane & 15) * LD_PP + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nb = 0; nb < NBW; nb += 2) {
+                const int n0 = warp * 8 * NBW + nb * 8;
+                if (n0 < R) {                                // the same for the whole warp
+                    uint32_t b[4];
+                    ld_ldsm_x4_trans(b, kt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch + n0 + ((lane >> 4) & 1) * 8);
+                    ld_mma(o[nb], a, b[0], b[1]);
+                    ld_mma(o[nb + 1], a, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();                                     // this buffer is loaded again in the next round
+    }
+    // the weight sums: over the quad, then over the warps (every warp has the same maxima)
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    }
+    if (t4 == 0) {
+        red[warp * LD_M + g] = l[0];
+        red[warp * LD_M + g + 8] = l[1];
+    }
+    __syncthreads();
+    const size_t slot = ((size_t)seq * nsplit + split) * nh;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = g + 8 * i, h = h0 + r;
+        if (h >= nh) continue;
+        float* dst = part_o + (slot + h) * R;
+#pragma unroll
+        for (int nb = 0; nb < NBW; ++nb) {
+            const int c = warp * 8 * NBW + nb * 8 + 2 * t4;
+            if (c < R) dst[c] = o[nb][2 * i];
+            if (c + 1 < R) dst[c + 1] = o[nb][2 * i + 1];
+        }
+        if (warp == 0 && t4 == 0) {
+            part_ml[(slot + h) * 2] = m[i];
+            part_ml[(slot + h) * 2 + 1] = red[r] + red[LD_M + r] + red[2 * LD_M + r] + red[3 * LD_M + r];
+        }
+    }
+}
+
+// one CTA per (sequence, head): the slices' sums weighed by exp(maximum - overall maximum), in slice order
+__global__ void latent_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                           bf16* __restrict__ out, const int* __restrict__ seq_start, int nh, int R,
+                                           int nsplit, const float* __restrict__ gate, long long gate_ld) {
+    const int seq = blockIdx.x, h = blockIdx.y;
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    const int row = seq_start[seq];
+    if (seq_start[seq + 1] - row != 1) return;
+    float mm = -FLT_MAX;
+    for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, part_ml[(((size_t)seq * nsplit + s) * nh + h) * 2]);
+    float den = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float* ml = part_ml + (((size_t)seq * nsplit + s) * nh + h) * 2;
+        den = fmaf(ml[1], expf(ml[0] - mm), den);
+    }
+    float f = 1.0f / den;
+    if (gate) f /= 1.0f + expf(-gate[(size_t)row * gate_ld + h]);
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float num = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            const size_t slot = ((size_t)seq * nsplit + s) * nh + h;
+            num = fmaf(part_o[slot * R + c], expf(part_ml[slot * 2] - mm), num);
+        }
+        out[((size_t)row * nh + h) * R + c] = __float2bfloat16_rn(num * f);
+    }
+}
+
+// Key slices per sequence: enough CTAs for the GPU (one CTA fills an SM's shared memory), no slice
+// shorter than two tiles of the longest context the step may hold.
+AP_EXPORT int ap_latent_decode_splits(int nseq, int nh, int max_context) {
+    const int groups = (nh + LD_M - 1) / LD_M;
+    const int tiles = (max_context > 0 ? max_context : 1) / LD_KT + 1;
+    int want = (148 + nseq * groups - 1) / (nseq * groups > 0 ? nseq * groups : 1);
+    const int most = tiles / 2 > 0 ? tiles / 2 : 1;
+    if (want > most) want = most;
+    if (want > 64) want = 64;
+    return want < 1 ? 1 : want;
+}
+
+// Whether the kernel takes these sizes (else the caller uses the general kernels).
+AP_EXPORT int ap_latent_decode_takes(int D, int R) {
+    const int D16 = (D + 15) & ~15;
+    const size_t smem = (size_t)(LD_M + 2 * LD_KT) * (D16 + 8) * 2 + LD_M * LD_PP * 2 + 4 * LD_M * 4;
+    return D > 0 && R > 0 && D % 8 == 0 && R % 8 == 0 && R <= D && R <= 512 && smem <= 220 * 1024;
+}
+
+AP_EXPORT int ap_latent_decode(const void* q, void* out, const void* cache, const int* block_table, int max_blocks,
+                               const int* seq_start, const int* positions, int nseq, int nh, int D, int R, int P,
+                               long long page_stride, float scale, const float* gate, long long gate_ld, int nsplit,
+                               float* scratch, long long scratch_floats, cudaStream_t stream) {
+    AP_REQUIRE(nseq >= 0 && nh > 0 && P > 0 && max_blocks > 0 && nsplit >= 1, "latent_decode: bad sizes");
+    AP_REQUIRE(ap_latent_decode_takes(D, R), "latent_decode: a record of %d with a value of %d is not one the kernel takes", D, R);
+    AP_REQUIRE(page_stride % 8 == 0 && ((uintptr_t)cache & 15) == 0 && ((uintptr_t)q & 15) == 0,
+               "latent_decode: queries and pages must be 16-byte aligned");
+    AP_REQUIRE(gate == nullptr || gate_ld >= nh, "latent_decode: bad gate stride");
+    AP_REQUIRE(scratch_floats >= (long long)nseq * nsplit * nh * (R + 2), "latent_decode: the scratch is too small");
+    if (nseq == 0) return AP_OK;
+    const int groups = (nh + LD_M - 1) / LD_M;
+    AP_REQUIRE(groups <= 65535 && nsplit <= 65535, "latent_decode: the grid is too large");
+    const int D16 = (D + 15) & ~15;
+    const size_t smem = (size_t)(LD_M + 2 * LD_KT) * (D16 + 8) * 2 + LD_M * LD_PP * 2 + 4 * LD_M * 4;
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)nseq * nsplit * nh * R;
+    const dim3 grid((unsigned)nseq, (unsigned)groups, (unsigned)nsplit);
+#define LAUNCH(NBW)                                                                                                    \
+    do {                                                                                                               \
+        auto kern = latent_decode_kernel<NBW>;                                                                         \
+        if (smem > 48 * 1024) {                                                                                        \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+            AP_REQUIRE(e == cudaSuccess, "latent_decode: cannot reserve %zu bytes of shared memory", smem);            \
+        }                                                                                                              \
+        AP_CHECK_PDL_LAUNCH("latent_decode",                                                                           \
+                            ap_launch_pdl(kern, grid, dim3(LD_THREADS), smem, stream, (const bf16*)q, (const bf16*)cache, \
+                                          block_table, max_blocks, seq_start, positions, nh, D, R, P, (size_t)page_stride, \
+                                          scale, nsplit, part_o, part_ml));                                            \
+    } while (0)
+    if (R <= 128) LAUNCH(4);
+    else if (R <= 256) LAUNCH(8);
+    else LAUNCH(16);
+#undef LAUNCH
+    AP_CHECK_PDL_LAUNCH("latent_decode_merge",
+                        ap_launch_pdl(latent_decode_merge_kernel, dim3((unsigned)nseq, (unsigned)nh), dim3(128), 0, stream,
+                                      (const float*)part_o, (const float*)part_ml, (bf16*)out, seq_start, nh, R, nsplit,
+                                      gate, gate_ld));
+    return AP_OK;
+}

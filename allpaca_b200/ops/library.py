@@ -59,6 +59,11 @@ _CORE_SIGNATURES = {
     # int ap_latent_gather(cache, dtype, page_stride, P, record, block_table, max_blocks, seq_start, context_lens,
     #                      nseq, out, where, width, total, stream)
     "ap_latent_gather": [_P, _I, _L, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _P],
+    # int ap_latent_decode(q, out, cache, block_table, max_blocks, seq_start, positions, nseq, nh, record, value,
+    #                      P, page_stride, scale, gate, gate_ld, nsplit, scratch, scratch_floats, stream)
+    "ap_latent_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _L, _F, _P, _L, _I, _P, _L, _P],
+    "ap_latent_decode_splits": [_I, _I, _I],
+    "ap_latent_decode_takes": [_I, _I],
     # int ap_causal_conv_silu(in, ld_in, col0, w, bias, state, state_stride, token_seq, seq_start, positions,
     #                         state_slots, out, T, nseq, C, taps, stream)
     "ap_causal_conv_silu": [_P, _L, _I, _P, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],

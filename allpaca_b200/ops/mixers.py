@@ -337,3 +337,43 @@ def latent_gather(cache_layer: torch.Tensor, block_table: torch.Tensor, seq_star
          cache_layer.shape[1], cache_layer.shape[2], block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(),
          context_lens.data_ptr(), int(num_seqs), out.data_ptr(), where.data_ptr(), where.shape[1], out.shape[0],
          stream_handle())
+
+
+def latent_decode_takes(record: int, value_dim: int) -> bool:
+    """Whether :func:`latent_decode` takes a record of ``record`` numbers whose first ``value_dim`` are the value."""
+    return bool(core().ap_latent_decode_takes(int(record), int(value_dim)))
+
+
+def latent_decode(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor,
+                  seq_start: torch.Tensor, positions: torch.Tensor, num_seqs: int, num_heads: int, record: int,
+                  value_dim: int, scale: float, gate: Optional[torch.Tensor], max_context: int, workspace) -> None:
+    """bfloat16 attention of the sequences that bring ONE row over pages ``[pages, P, record]`` whose
+    records are every head's key and, in their first ``value_dim`` numbers, every head's value:
+    ``q [T, heads*record]`` -> ``out [T, heads*value_dim]`` times ``sigmoid(gate[t, h])`` (rows of other
+    sequences are left alone).  All heads of a sequence share the key tiles on the tensor cores; the
+    keys are cut into slices by ``max_context`` (the longest context the step may hold), whose partial
+    results wait in a buffer taken from ``workspace``."""
+    _check(q, "q", torch.bfloat16, 2)
+    _check(out, "out", torch.bfloat16, 2)
+    T = q.shape[0]
+    if q.shape[1] != num_heads * record or tuple(out.shape) != (T, num_heads * value_dim):
+        raise KernelError("latent_decode: q/out do not match the heads")
+    if cache_layer.dtype != torch.bfloat16:
+        raise KernelError("latent_decode: the pages must be bfloat16")
+    P, page_stride = _kv_pages(cache_layer, 1, record, "latent_decode")
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(seq_start, "seq_start", torch.int32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    gptr, gld = 0, 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.dim() != 2 or gate.shape[0] < T or gate.shape[1] != num_heads \
+                or gate.stride(1) != 1 or not gate.is_cuda:
+            raise KernelError("latent_decode: the gate must be 32-bit [T, heads] with contiguous rows")
+        gptr, gld = gate.data_ptr(), gate.stride(0)
+    lib = core()
+    nsplit = int(lib.ap_latent_decode_splits(int(num_seqs), int(num_heads), int(max_context)))
+    need = num_seqs * nsplit * num_heads * (value_dim + 2)
+    scratch = workspace.get("latent_decode.partial", (need,), torch.float32)
+    call(lib, "ap_latent_decode", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(), block_table.data_ptr(),
+         block_table.shape[1], seq_start.data_ptr(), positions.data_ptr(), int(num_seqs), int(num_heads), int(record),
+         int(value_dim), P, page_stride, float(scale), gptr, gld, nsplit, scratch.data_ptr(), need, stream_handle())

@@ -153,11 +153,17 @@ class LatentAttention(Mixer):
             qa = ws.get("lattn.qa", (T, self.nh * rec), dt)
             ops.head_project(q, self.uk, qa, self.nh, tail=self.rot, tail_dims=self.rot_dims, cos_sin=cos_sin)
             ol = ws.get("lattn.ol", (T, self.nh * self.R), dt)
-            ops.attention_window_bias(qa, ol, cache.pages, table, step.seq_start, step.positions, step.num_seqs,
-                                      self.nh, 1, rec, self.R, self.scale, 0, None, None,
-                                      single_rows=dt == torch.bfloat16 and singles,
-                                      other_rows=step.max_query_len != 1 and not per_head, bias=None, gate=gate,
-                                      record=rec, value_offset=0)
+            # sequences that bring one row: all heads together against shared key tiles on the tensor cores
+            fast = dt == torch.bfloat16 and singles and ops.latent_decode_takes(rec, self.R)
+            if fast:
+                ops.latent_decode(qa, ol, cache.pages, table, step.seq_start, step.positions, step.num_seqs, self.nh,
+                                  rec, self.R, self.scale, gate, step.max_decode_context_len or step.max_context_len, ws)
+            others = step.max_query_len != 1 and not per_head
+            if others or not fast:
+                ops.attention_window_bias(qa, ol, cache.pages, table, step.seq_start, step.positions, step.num_seqs,
+                                          self.nh, 1, rec, self.R, self.scale, 0, None, None,
+                                          single_rows="skip" if fast else (dt == torch.bfloat16 and singles),
+                                          other_rows=others, bias=None, gate=gate, record=rec, value_offset=0)
             ops.head_project(ol, self.uv, ov, self.nh)
         if per_head:
             # the sequences that bring several rows, on per-head keys and values of all their tokens so far

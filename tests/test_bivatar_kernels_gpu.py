@@ -266,3 +266,56 @@ def test_query_and_key_norm_with_weights(dtype):
         slot = pages[[4, 2, 5, 0][p // P], :, p % P].float().cpu()
         close(slot[:, :D], keys[i], tol, ("key", p))
         close(slot[:, D:], qkv[i, (H + G) * D:(H + G) * D + G * E].view(G, E), tol, ("value", p))
+
+
+@pytest.mark.parametrize("H,R,rot,P", [(3, 48, 16, 8), (16, 512, 64, 16), (20, 136, 16, 16), (40, 64, 32, 32), (8, 256, 8, 16)])
+@pytest.mark.parametrize("max_context", [1, 4096])
+def test_single_rows_in_the_latent_space_on_the_tensor_cores(H, R, rot, P, max_context):
+    """Sequences of 1 to 2500 tokens that each bring their last row, beside one that brings two rows (left
+    alone): all heads against the shared records, keys cut into one slice or many.  In every sequence
+    one head looks hard at one key: the first, the last of a tile of 64, far back."""
+    from allpaca_b200 import ops
+    from allpaca_b200.parts import Workspace
+    g = torch.Generator().manual_seed(H + R)
+    D = R + rot
+    lens = [1, 64, 65, 2, 700, 2500]
+    rows_of = [1, 1, 1, 2, 1, 1]
+    scale = 1.0 / math.sqrt(D)
+    recs, qs, gates, table, pages_all, want, positions, starts = [], [], [], [], [], [], [], [0]
+    base = 0
+    for n, rows in zip(lens, rows_of):
+        rec = torch.randn(n, D, generator=g).to(torch.bfloat16).double()
+        q = torch.randn(rows, H, D, generator=g)
+        key = {1: 0, 64: 63, 65: 64, 2: 0, 700: 63, 2500: 1234}[n]
+        q[-1, n % H] = 5.0 * math.sqrt(D) * rec[key].float() / rec[key].norm()
+        q = q.to(torch.bfloat16).double()
+        gate = 2.0 * torch.randn(rows, H, generator=g)
+        if rows == 1:
+            s = torch.einsum("hd,nd->hn", q[0], rec) * scale
+            want.append((torch.softmax(s, dim=-1) @ rec[:, :R]) * torch.sigmoid(gate.double()[0])[:, None])
+        else:
+            want.append(torch.full((rows, H, R), float("nan"), dtype=torch.float64).view(rows * H, R))
+        npg = -(-n // P)
+        pg, row = paged(rec[:, None, :], P, shuffled(npg, base))
+        pages_all.append(pg[base:, 0])
+        table.append(row)
+        base += npg
+        qs.append(q)
+        gates.append(gate)
+        positions += list(range(n - rows, n))
+        starts.append(starts[-1] + rows)
+    pages = torch.cat(pages_all).to(torch.bfloat16).to(DEV)
+    width = max(len(r) for r in table)
+    bt = i32([r + [-1] * (width - len(r)) for r in table])
+    T = starts[-1]
+    q = torch.cat(qs).reshape(T, H * D).to(torch.bfloat16).to(DEV).contiguous()
+    gate = torch.cat(gates).to(DEV).contiguous()
+    out = torch.full((T, H * R), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.latent_decode(q, out, pages, bt, i32(starts), i32(positions), len(lens), H, D, R, scale, gate, max_context,
+                      Workspace(torch.device(DEV)))
+    got = out.float().cpu().view(T, H, R)
+    for s, rows in enumerate(rows_of):
+        if rows == 1:
+            close(got[starts[s]], want[s], 2e-2, ("sequence of", lens[s]))
+        else:
+            assert torch.isnan(got[starts[s]:starts[s + 1]]).all(), "rows of a sequence that brings two were written"
