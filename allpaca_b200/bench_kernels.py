@@ -3,6 +3,8 @@
     python -m allpaca_b200.bench_kernels gemm --m 8 --n 6144 --k 4096 [--splits S] [--partials] [--swiglu]
     python -m allpaca_b200.bench_kernels attention --batch 8 --context 4096
     python -m allpaca_b200.bench_kernels prefill-attention --tokens 2048
+    python -m allpaca_b200.bench_kernels latent-decode --batch 8 --context 4096   # single rows in a shared latent
+    python -m allpaca_b200.bench_kernels latent-prefill --tokens 2048             # a prompt on per-head keys and values
     python -m allpaca_b200.bench_kernels versus-reference      # a table: ours against the reference's own kernels
 
 Each call works on the next of several copies of its large operand (together larger than
@@ -173,6 +175,57 @@ def bench_prefill_attention(args) -> dict:
     us = _time(fn, args.iters, args.warmup, not args.no_graph)
     flops = 4.0 * nh * hd * T * (T + 1) / 2
     return {"kernel": "attention_tile" if args.mma_sync else "attention_tcgen05", "query_tiles": args.query_tiles, "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
+            "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
+
+
+def bench_latent_decode(args) -> dict:
+    """Sequences that bring one row each, all heads against the records ``[latent | rotated key part]`` that
+    every head shares (``ops.latent_decode``: the tensor-core kernel and its merge)."""
+    from allpaca_b200 import ops
+    from allpaca_b200.parts import Workspace
+    B, C, nh, R, rot, P = args.batch, args.context, args.heads, args.kv_rank, args.rot_dim, args.page_size
+    D = R + rot
+    pages_per = -(-C // P)
+    per = B * C * D * 2
+    copies = max(2, int(math.ceil(300e6 / per)))
+    caches = [torch.randn(B * pages_per, P, D, device="cuda", dtype=torch.bfloat16) for _ in range(copies)]
+    table = torch.arange(B * pages_per, device="cuda", dtype=torch.int32).view(B, pages_per)
+    q = torch.randn(B, nh * D, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(B, nh * R, device="cuda", dtype=torch.bfloat16)
+    gate = torch.randn(B, nh, device="cuda")
+    start = torch.arange(B + 1, device="cuda", dtype=torch.int32)
+    pos = torch.full((B,), C - 1, device="cuda", dtype=torch.int32)
+    ws = Workspace(torch.device("cuda"))
+
+    def fn(i):
+        ops.latent_decode(q, out, caches[i % copies], table, start, pos, B, nh, D, R, 1.0 / math.sqrt(D), gate, C, ws)
+    us = _time(fn, args.iters, args.warmup, not args.no_graph)
+    flops = 2.0 * B * C * nh * (D + R)
+    return {"kernel": "latent_decode+merge", "batch": B, "context": C, "heads": nh, "kv_rank": R, "rot_dim": rot,
+            "us": round(us, 2), "GBps": round(per / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 2)}
+
+
+def bench_latent_prefill(args) -> dict:
+    """One prompt on per-head keys and values ``[token][head][key | rotated part | value]`` (what the latent
+    mixer's product forms for prompt portions): the tensor-core kernel of ``ops.attention_window_bias`` with
+    pages of one token."""
+    from allpaca_b200 import ops
+    T, nh, dk, dv = args.tokens, args.heads, args.head_dim + args.rot_dim, args.value_dim
+    kv = torch.randn(T, nh, 1, dk + dv, device="cuda", dtype=torch.bfloat16)
+    where = torch.arange(T, device="cuda", dtype=torch.int32).view(1, T)
+    q = torch.randn(T, nh * dk, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(T, nh * dv, device="cuda", dtype=torch.bfloat16)
+    gate = torch.randn(T, nh, device="cuda")
+    start = torch.tensor([0, T], device="cuda", dtype=torch.int32)
+    pos = torch.arange(T, device="cuda", dtype=torch.int32)
+
+    def fn(i):
+        ops.attention_window_bias(q, out, kv, where, start, pos, 1, nh, nh, dk, dv, 1.0 / math.sqrt(dk), 0, None, None,
+                                  single_rows=False, other_rows=True, bias=None, gate=gate, record=dk + dv,
+                                  value_offset=dk)
+    us = _time(fn, args.iters, args.warmup, not args.no_graph)
+    flops = 2.0 * nh * (dk + dv) * T * (T + 1) / 2
+    return {"kernel": "attention_window_bias_mma", "tokens": T, "heads": nh, "key_dim": dk, "value_dim": dv,
             "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
@@ -392,12 +445,27 @@ def main(argv=None) -> int:
     s.add_argument("--top-k", type=int, default=40, help="0: off")
     s.add_argument("--top-p", type=float, default=0.95, help="1: off")
     s.add_argument("--spread", type=float, default=3.0, help="standard deviation of the random logits")
+    for name in ("latent-decode", "latent-prefill"):
+        s = sub.add_parser(name)
+        s.add_argument("--iters", type=int, default=50)
+        s.add_argument("--warmup", type=int, default=5)
+        s.add_argument("--no-graph", action="store_true", help="launch from the host (for ncu)")
+        s.add_argument("--heads", type=int, default=16)
+        s.add_argument("--kv-rank", type=int, default=512)
+        s.add_argument("--rot-dim", type=int, default=64)
+        s.add_argument("--head-dim", type=int, default=128, help="unrotated query/key dimensions per head")
+        s.add_argument("--value-dim", type=int, default=128)
+        s.add_argument("--page-size", type=int, default=16)
+        s.add_argument("--batch", type=int, default=8)
+        s.add_argument("--context", type=int, default=4096)
+        s.add_argument("--tokens", type=int, default=2048)
     s = sub.add_parser("versus-reference")
     s.add_argument("--iters", type=int, default=20)
     s.add_argument("--warmup", type=int, default=3)
     args = p.parse_args(argv)
     fn = {"gemm": bench_gemm, "attention": bench_attention, "prefill-attention": bench_prefill_attention,
-          "sampling": bench_sampling, "versus-reference": bench_versus_reference}[args.what]
+          "sampling": bench_sampling, "versus-reference": bench_versus_reference,
+          "latent-decode": bench_latent_decode, "latent-prefill": bench_latent_prefill}[args.what]
     print(json.dumps(fn(args)))
     return 0
 

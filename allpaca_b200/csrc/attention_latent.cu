@@ -116,20 +116,24 @@ AP_EXPORT int ap_latent_prepare(const float* in, long long ld, int q0, int Q, co
 }
 
 // ---------------------------------------------------------------------------------------
-// out[t, h, n] = sum_k in[t, h, k] W[h, k, n].  A CTA takes HP_ROWS rows of one head and 128
-// columns; the rows' inputs wait in shared memory, every thread owns one column and walks k
-// upwards (neighbouring threads read neighbouring weights), so an output is one thread's
-// 32-bit sum in a fixed order whatever else the step holds.
+// out[t, h, n] = sum_k in[t, h, k] W[h, k, n].  A CTA takes HP_ROWS rows of one head and HP_COLS
+// columns; the rows' inputs wait in shared memory; thread (slice, column) walks its quarter of k
+// upwards (neighbouring threads read neighbouring weights, four slices of k in flight at once:
+// with few rows the walk is a chain of loads, not arithmetic), and the slices' sums are added in
+// slice order.  So an output is a 32-bit sum in a fixed order whatever else the step holds.
 // ---------------------------------------------------------------------------------------
 #define HP_ROWS 8
-#define HP_THREADS 128
+#define HP_COLS 32
+#define HP_SLICES 4
+#define HP_THREADS (HP_COLS * HP_SLICES)
 
 template <typename TI, typename TW, typename TO>
 __global__ void __launch_bounds__(HP_THREADS)
 head_project_kernel(const TI* __restrict__ in, long long in_ld, int in_hs, const TW* __restrict__ w,
                     TO* __restrict__ out, long long out_ld, int out_hs, int T, int K, int N, int tail, int half,
                     const float2* __restrict__ cos_sin) {
-    extern __shared__ __align__(16) float in_s[];            // [HP_ROWS][K]
+    extern __shared__ __align__(16) float in_s[];            // [HP_ROWS][K], then [HP_SLICES][HP_ROWS][HP_COLS]
+    float* part = in_s + HP_ROWS * K;
     const int row0 = blockIdx.x * HP_ROWS, h = blockIdx.y;
     const int rows = min(HP_ROWS, T - row0);
     ap_pdl_trigger();
@@ -139,26 +143,41 @@ head_project_kernel(const TI* __restrict__ in, long long in_ld, int in_hs, const
         in_s[i] = r < rows ? ap_to_float(in[(size_t)(row0 + r) * in_ld + (size_t)h * in_hs + k]) : 0.f;
     }
     __syncthreads();
-    const int n = blockIdx.z * HP_THREADS + threadIdx.x;
+    const int col = threadIdx.x % HP_COLS, slice = threadIdx.x / HP_COLS;
+    const int n = blockIdx.z * HP_COLS + col;
+    float acc[HP_ROWS];
+#pragma unroll
+    for (int r = 0; r < HP_ROWS; ++r) acc[r] = 0.f;
     if (n < N) {
-        float acc[HP_ROWS];
-#pragma unroll
-        for (int r = 0; r < HP_ROWS; ++r) acc[r] = 0.f;
         if (w == nullptr) {                                  // no matrix: the numbers pass as they are
+            if (slice == 0) {
 #pragma unroll
-            for (int r = 0; r < HP_ROWS; ++r) acc[r] = in_s[r * K + n];
+                for (int r = 0; r < HP_ROWS; ++r) acc[r] = in_s[r * K + n];
+            }
         } else {
+            const int per = (K + HP_SLICES - 1) / HP_SLICES;
+            const int k0 = slice * per, k1 = min(K, k0 + per);
             const TW* wc = w + (size_t)h * K * N + n;
-#pragma unroll 4
-            for (int k = 0; k < K; ++k) {
+#pragma unroll 8
+            for (int k = k0; k < k1; ++k) {
                 const float wv = ap_to_float(wc[(size_t)k * N]);
 #pragma unroll
                 for (int r = 0; r < HP_ROWS; ++r) acc[r] = fmaf(in_s[r * K + k], wv, acc[r]);
             }
         }
+    }
 #pragma unroll
-        for (int r = 0; r < HP_ROWS; ++r)
-            if (r < rows) out[(size_t)(row0 + r) * out_ld + (size_t)h * out_hs + n] = ap_from_float<TO>(acc[r]);
+    for (int r = 0; r < HP_ROWS; ++r) part[(slice * HP_ROWS + r) * HP_COLS + col] = acc[r];
+    __syncthreads();
+    for (int i = threadIdx.x; i < HP_ROWS * HP_COLS; i += HP_THREADS) {
+        const int r = i / HP_COLS, c = i - r * HP_COLS;
+        const int nn = blockIdx.z * HP_COLS + c;
+        if (r < rows && nn < N) {
+            float v = part[r * HP_COLS + c];
+#pragma unroll
+            for (int sl = 1; sl < HP_SLICES; ++sl) v += part[(sl * HP_ROWS + r) * HP_COLS + c];
+            out[(size_t)(row0 + r) * out_ld + (size_t)h * out_hs + nn] = ap_from_float<TO>(v);
+        }
     }
     if (tail > 0 && blockIdx.z == 0) {
         const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -180,9 +199,9 @@ AP_EXPORT int ap_head_project(const void* in, int in_dtype, long long in_ld, int
     AP_REQUIRE(tail_dims % 2 == 0 && tail_dims >= 0 && tail_dims <= tail && (tail_dims == 0 || cos_sin),
                "head_project: %d rotated dimensions of a tail of %d", tail_dims, tail);
     if (T == 0) return AP_OK;
-    const size_t smem = (size_t)HP_ROWS * K * sizeof(float);
+    const size_t smem = ((size_t)HP_ROWS * K + (size_t)HP_SLICES * HP_ROWS * HP_COLS) * sizeof(float);
     AP_REQUIRE(smem <= 200 * 1024, "head_project: K=%d does not fit shared memory", K);
-    const dim3 grid((unsigned)((T + HP_ROWS - 1) / HP_ROWS), (unsigned)H, (unsigned)((N + HP_THREADS - 1) / HP_THREADS));
+    const dim3 grid((unsigned)((T + HP_ROWS - 1) / HP_ROWS), (unsigned)H, (unsigned)((N + HP_COLS - 1) / HP_COLS));
 #define LAUNCH(TI, TW, TO)                                                                                             \
     do {                                                                                                               \
         auto kern = head_project_kernel<TI, TW, TO>;                                                                   \

@@ -5,9 +5,9 @@
 // same keys: a CTA takes 16 heads of one sequence and a slice of its keys, and every key tile that
 // reaches shared memory serves all 16 rows on the tensor cores (mma.sync m16n8k16, 32-bit sums):
 //
-//   S [16 heads x 64 keys] = Q [16 x D] K^T      warp w: keys 16w .. 16w+15 of the tile
-//   online softmax over the tile                  row maxima of the four warps meet in shared memory
-//   O [16 x R] += P [16 x 64] V [64 x R]          warp w: its quarter of the R columns; V is the same
+//   S [16 heads x 64 keys] = Q [16 x D] K^T      warp w of eight: keys 8w .. 8w+7 of the tile
+//   online softmax over the tile                  row maxima of the eight warps meet in shared memory
+//   O [16 x R] += P [16 x 64] V [64 x R]          warp w: its eighth of the R columns; V is the same
 //                                                 tile, read transposed (ldmatrix.trans)
 //
 // Key tiles come by cp.async into two buffers, the next one loading while this one is used.  The
@@ -16,8 +16,9 @@
 #include "common.cuh"
 #include <float.h>
 
-#define LD_THREADS 128
-#define LD_KT 64              // keys per tile
+#define LD_WARPS 8
+#define LD_THREADS (LD_WARPS * 32)
+#define LD_KT 64              // keys per tile: eight to a warp
 #define LD_M 16               // heads per CTA
 #define LD_PP 72              // row pitch of the probabilities in shared memory (64 + 8)
 
@@ -48,7 +49,7 @@ __device__ __forceinline__ uint32_t ld_pack(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// NBW: blocks of 8 value columns per warp (R <= 32 NBW)
+// NBW: blocks of 8 value columns per warp (R <= 64 NBW)
 template <int NBW>
 __global__ void __launch_bounds__(LD_THREADS)
 latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, const int* __restrict__ block_table,
@@ -67,30 +68,38 @@ latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
     bf16* q_s = reinterpret_cast<bf16*>(ld_smem);            // [16][pitch]
     bf16* k_s = q_s + LD_M * pitch;                          // [2][64][pitch]
     bf16* p_s = k_s + 2 * LD_KT * pitch;                     // [16][LD_PP]
-    float* red = reinterpret_cast<float*>(p_s + LD_M * LD_PP);   // [4][16]
+    float* red = reinterpret_cast<float*>(p_s + LD_M * LD_PP);   // [LD_WARPS][16]
     const int* table = block_table + (size_t)seq * max_blocks;
     const int tiles = qpos / LD_KT + 1;
     const int per = (tiles + nsplit - 1) / nsplit;
     const int t0 = split * per, t1 = min(tiles, t0 + per);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
-    const int chunks = D16 / 8;
+    const int chunks = D16 / 8, dchunks = D / 8;             // 16-byte runs of a padded row, and of a record
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    for (int i = threadIdx.x; i < LD_M * chunks; i += LD_THREADS) {
-        const int r = i / chunks, c = (i - r * chunks) * 8;
-        uint4 v = zero;
-        if (h0 + r < nh && c < D) v = *reinterpret_cast<const uint4*>(q + ((size_t)row * nh + h0 + r) * D + c);
-        *reinterpret_cast<uint4*>(q_s + r * pitch + c) = v;
+    for (int r = warp; r < LD_M; r += LD_WARPS) {
+        const bf16* src = q + ((size_t)row * nh + h0 + r) * D;
+        for (int c = lane; c < chunks; c += 32)
+            *reinterpret_cast<uint4*>(q_s + r * pitch + c * 8) =
+                (h0 + r < nh && c < dchunks) ? *reinterpret_cast<const uint4*>(src + c * 8) : zero;
     }
+    // a warp brings eight keys of a tile: the page and slot of a key are found once, the lanes share its record
     auto load_tile = [&](int tile, int stage) {
         bf16* dst = k_s + (size_t)stage * LD_KT * pitch;
-        for (int i = threadIdx.x; i < LD_KT * chunks; i += LD_THREADS) {
-            const int j = i / chunks, c = (i - j * chunks) * 8;
+#pragma unroll 2
+        for (int jj = 0; jj < LD_KT / LD_WARPS; ++jj) {
+            const int j = jj * LD_WARPS + warp;
             const int kp = tile * LD_KT + j;
-            bf16* d = dst + j * pitch + c;
-            if (kp <= qpos && c < D)
-                ld_cp_async16(d, cache + (size_t)table[kp / P] * page_stride + (size_t)(kp % P) * D + c);
-            else
-                *reinterpret_cast<uint4*>(d) = zero;         // keys behind the row and the padding: finite, weight zero
+            bf16* d = dst + j * pitch;
+            if (kp <= qpos) {
+                const bf16* src = cache + (size_t)table[kp / P] * page_stride + (size_t)(kp % P) * D;
+                for (int c = lane; c < chunks; c += 32) {
+                    if (c < dchunks) ld_cp_async16(d + c * 8, src + c * 8);
+                    else *reinterpret_cast<uint4*>(d + c * 8) = zero;
+                }
+            } else {
+                // keys behind the row: finite, weight zero
+                for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(d + c * 8) = zero;
+            }
         }
         ld_cp_async_commit();
     };
@@ -109,26 +118,32 @@ latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
         }
         __syncthreads();                                     // the tile (and, the first time, the queries) are there
         const bf16* kt = k_s + (size_t)stage * LD_KT * pitch;
-        float s[2][4];
-#pragma unroll
-        for (int nb = 0; nb < 2; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
-        for (int ks = 0; ks < D16 / 16; ++ks) {
+        // S for keys 8 warp .. 8 warp + 7: two sums that take the blocks of 16 dimensions in turn
+        float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+        const bf16* qa = q_s + (lane & 15) * pitch + (lane >> 4) * 8;
+        const bf16* kb = kt + (8 * warp + (lane & 7)) * pitch + (lane >> 3) * 8;
+        int ks = 0;
+        for (; ks + 1 < D16 / 16; ks += 2) {
+            uint32_t a[4], a2[4], b[4];
+            ld_ldsm_x4(b, kb + ks * 16);                     // this key block, dimensions 0-7, 8-15, 16-23, 24-31 of the pair
+            ld_ldsm_x4(a, qa + ks * 16);
+            ld_ldsm_x4(a2, qa + ks * 16 + 16);
+            ld_mma(s, a, b[0], b[1]);
+            ld_mma(s2, a2, b[2], b[3]);
+        }
+        if (ks < D16 / 16) {                                 // an odd block left: the row's padding is read and not used
             uint32_t a[4], b[4];
-            ld_ldsm_x4(a, q_s + (lane & 15) * pitch + ks * 16 + (lane >> 4) * 8);
-            ld_ldsm_x4(b, kt + (16 * warp + (lane & 7) + ((lane >> 4) & 1) * 8) * pitch + ks * 16 + ((lane >> 3) & 1) * 8);
-            ld_mma(s[0], a, b[0], b[1]);
-            ld_mma(s[1], a, b[2], b[3]);
+            ld_ldsm_x4(b, kb + ks * 16 - 16);
+            ld_ldsm_x4(a, qa + ks * 16);
+            ld_mma(s, a, b[2], b[3]);
         }
         float mx[2] = {-FLT_MAX, -FLT_MAX};
 #pragma unroll
-        for (int nb = 0; nb < 2; ++nb) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int kp = tile * LD_KT + 16 * warp + nb * 8 + 2 * t4 + (e & 1);
-                const float v = kp <= qpos ? s[nb][e] * scale : -FLT_MAX;
-                s[nb][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
-            }
+        for (int e = 0; e < 4; ++e) {
+            const int kp = tile * LD_KT + 8 * warp + 2 * t4 + (e & 1);
+            const float v = kp <= qpos ? (s[e] + s2[e]) * scale : -FLT_MAX;
+            s[e] = v;
+            mx[e >> 1] = fmaxf(mx[e >> 1], v);
         }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -144,25 +159,23 @@ latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int r = g + 8 * i;
-            const float mm = fmaxf(fmaxf(red[r], red[LD_M + r]), fmaxf(red[2 * LD_M + r], red[3 * LD_M + r]));
+            float mm = red[r];
+#pragma unroll
+            for (int w = 1; w < LD_WARPS; ++w) mm = fmaxf(mm, red[w * LD_M + r]);
             const float m_new = fmaxf(m[i], mm);
             alpha[i] = __expf(m[i] - m_new);
             m[i] = m_new;
             l[i] *= alpha[i];
         }
 #pragma unroll
-        for (int nb = 0; nb < 2; ++nb) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                // the weight is rounded to bfloat16 for the second product: the fast exponential's error is far below that
-                const float p = s[nb][e] > -FLT_MAX ? __expf(s[nb][e] - m[e >> 1]) : 0.f;
-                s[nb][e] = p;
-                l[e >> 1] += p;
-            }
-            const int c = 16 * warp + nb * 8 + 2 * t4;
-            *reinterpret_cast<uint32_t*>(p_s + g * LD_PP + c) = ld_pack(s[nb][0], s[nb][1]);
-            *reinterpret_cast<uint32_t*>(p_s + (g + 8) * LD_PP + c) = ld_pack(s[nb][2], s[nb][3]);
+        for (int e = 0; e < 4; ++e) {
+            // the weight is rounded to bfloat16 for the second product: the fast exponential's error is far below that
+            const float p = s[e] > -FLT_MAX ? __expf(s[e] - m[e >> 1]) : 0.f;
+            s[e] = p;
+            l[e >> 1] += p;
         }
+        *reinterpret_cast<uint32_t*>(p_s + g * LD_PP + 8 * warp + 2 * t4) = ld_pack(s[0], s[1]);
+        *reinterpret_cast<uint32_t*>(p_s + (g + 8) * LD_PP + 8 * warp + 2 * t4) = ld_pack(s[2], s[3]);
 #pragma unroll
         for (int i = 0; i < NBW; ++i) {
             o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
@@ -210,36 +223,59 @@ latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
             if (c + 1 < R) dst[c + 1] = o[nb][2 * i + 1];
         }
         if (warp == 0 && t4 == 0) {
+            float sum = red[r];
+#pragma unroll
+            for (int w = 1; w < LD_WARPS; ++w) sum += red[w * LD_M + r];
             part_ml[(slot + h) * 2] = m[i];
-            part_ml[(slot + h) * 2 + 1] = red[r] + red[LD_M + r] + red[2 * LD_M + r] + red[3 * LD_M + r];
+            part_ml[(slot + h) * 2 + 1] = sum;
         }
     }
 }
 
-// one CTA per (sequence, head): the slices' sums weighed by exp(maximum - overall maximum), in slice order
-__global__ void latent_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                           bf16* __restrict__ out, const int* __restrict__ seq_start, int nh, int R,
-                                           int nsplit, const float* __restrict__ gate, long long gate_ld) {
+// one CTA per (sequence, head): the slices' sums weighed by exp(maximum - overall maximum), in slice order;
+// the weights are formed once, and a thread's loads of its column are independent of one another
+#define LD_MAX_SPLITS 64
+__global__ void __launch_bounds__(128)
+latent_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                           bf16* __restrict__ out, const int* __restrict__ seq_start, int nh, int R,
+                           int nsplit, const float* __restrict__ gate, long long gate_ld) {
+    __shared__ float w_s[LD_MAX_SPLITS];
+    __shared__ float f_s;
     const int seq = blockIdx.x, h = blockIdx.y;
     ap_pdl_trigger();
     ap_pdl_wait();
     const int row = seq_start[seq];
     if (seq_start[seq + 1] - row != 1) return;
-    float mm = -FLT_MAX;
-    for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, part_ml[(((size_t)seq * nsplit + s) * nh + h) * 2]);
-    float den = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float* ml = part_ml + (((size_t)seq * nsplit + s) * nh + h) * 2;
-        den = fmaf(ml[1], expf(ml[0] - mm), den);
-    }
-    float f = 1.0f / den;
-    if (gate) f /= 1.0f + expf(-gate[(size_t)row * gate_ld + h]);
-    for (int c = threadIdx.x; c < R; c += blockDim.x) {
-        float num = 0.f;
-        for (int s = 0; s < nsplit; ++s) {
-            const size_t slot = ((size_t)seq * nsplit + s) * nh + h;
-            num = fmaf(part_o[slot * R + c], expf(part_ml[slot * 2] - mm), num);
+    const size_t slot0 = (size_t)seq * nsplit * nh + h;      // slice s: slot0 + s * nh
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float m0 = -FLT_MAX, m1 = -FLT_MAX, l0 = 0.f, l1 = 0.f;
+        if (lane < nsplit) {
+            m0 = part_ml[(slot0 + (size_t)lane * nh) * 2];
+            l0 = part_ml[(slot0 + (size_t)lane * nh) * 2 + 1];
         }
+        if (lane + 32 < nsplit) {
+            m1 = part_ml[(slot0 + (size_t)(lane + 32) * nh) * 2];
+            l1 = part_ml[(slot0 + (size_t)(lane + 32) * nh) * 2 + 1];
+        }
+        const float mm = ap_warp_max(fmaxf(m0, m1));
+        const float w0 = lane < nsplit ? expf(m0 - mm) : 0.f, w1 = lane + 32 < nsplit ? expf(m1 - mm) : 0.f;
+        w_s[lane] = w0;
+        w_s[lane + 32] = w1;
+        const float den = ap_warp_sum(fmaf(l0, w0, l1 * w1));
+        if (lane == 0) {
+            float f = 1.0f / den;
+            if (gate) f /= 1.0f + expf(-gate[(size_t)row * gate_ld + h]);
+            f_s = f;
+        }
+    }
+    __syncthreads();
+    const float f = f_s;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        const float* src = part_o + slot0 * R + c;
+        float num = 0.f;
+#pragma unroll 8
+        for (int s = 0; s < nsplit; ++s) num = fmaf(src[(size_t)s * nh * R], w_s[s], num);
         out[((size_t)row * nh + h) * R + c] = __float2bfloat16_rn(num * f);
     }
 }
@@ -252,14 +288,14 @@ AP_EXPORT int ap_latent_decode_splits(int nseq, int nh, int max_context) {
     int want = (148 + nseq * groups - 1) / (nseq * groups > 0 ? nseq * groups : 1);
     const int most = tiles / 2 > 0 ? tiles / 2 : 1;
     if (want > most) want = most;
-    if (want > 64) want = 64;
+    if (want > 32) want = 32;                                // the merge adds them up one after another
     return want < 1 ? 1 : want;
 }
 
 // Whether the kernel takes these sizes (else the caller uses the general kernels).
 AP_EXPORT int ap_latent_decode_takes(int D, int R) {
     const int D16 = (D + 15) & ~15;
-    const size_t smem = (size_t)(LD_M + 2 * LD_KT) * (D16 + 8) * 2 + LD_M * LD_PP * 2 + 4 * LD_M * 4;
+    const size_t smem = (size_t)(LD_M + 2 * LD_KT) * (D16 + 8) * 2 + LD_M * LD_PP * 2 + LD_WARPS * LD_M * 4;
     return D > 0 && R > 0 && D % 8 == 0 && R % 8 == 0 && R <= D && R <= 512 && smem <= 220 * 1024;
 }
 
@@ -267,7 +303,8 @@ AP_EXPORT int ap_latent_decode(const void* q, void* out, const void* cache, cons
                                const int* seq_start, const int* positions, int nseq, int nh, int D, int R, int P,
                                long long page_stride, float scale, const float* gate, long long gate_ld, int nsplit,
                                float* scratch, long long scratch_floats, cudaStream_t stream) {
-    AP_REQUIRE(nseq >= 0 && nh > 0 && P > 0 && max_blocks > 0 && nsplit >= 1, "latent_decode: bad sizes");
+    AP_REQUIRE(nseq >= 0 && nh > 0 && P > 0 && max_blocks > 0 && nsplit >= 1 && nsplit <= LD_MAX_SPLITS,
+               "latent_decode: bad sizes (at most %d key slices)", LD_MAX_SPLITS);
     AP_REQUIRE(ap_latent_decode_takes(D, R), "latent_decode: a record of %d with a value of %d is not one the kernel takes", D, R);
     AP_REQUIRE(page_stride % 8 == 0 && ((uintptr_t)cache & 15) == 0 && ((uintptr_t)q & 15) == 0,
                "latent_decode: queries and pages must be 16-byte aligned");
@@ -277,7 +314,7 @@ AP_EXPORT int ap_latent_decode(const void* q, void* out, const void* cache, cons
     const int groups = (nh + LD_M - 1) / LD_M;
     AP_REQUIRE(groups <= 65535 && nsplit <= 65535, "latent_decode: the grid is too large");
     const int D16 = (D + 15) & ~15;
-    const size_t smem = (size_t)(LD_M + 2 * LD_KT) * (D16 + 8) * 2 + LD_M * LD_PP * 2 + 4 * LD_M * 4;
+    const size_t smem = (size_t)(LD_M + 2 * LD_KT) * (D16 + 8) * 2 + LD_M * LD_PP * 2 + LD_WARPS * LD_M * 4;
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)nseq * nsplit * nh * R;
     const dim3 grid((unsigned)nseq, (unsigned)groups, (unsigned)nsplit);
@@ -293,9 +330,9 @@ AP_EXPORT int ap_latent_decode(const void* q, void* out, const void* cache, cons
                                           block_table, max_blocks, seq_start, positions, nh, D, R, P, (size_t)page_stride, \
                                           scale, nsplit, part_o, part_ml));                                            \
     } while (0)
-    if (R <= 128) LAUNCH(4);
-    else if (R <= 256) LAUNCH(8);
-    else LAUNCH(16);
+    if (R <= 128) LAUNCH(2);
+    else if (R <= 256) LAUNCH(4);
+    else LAUNCH(8);
 #undef LAUNCH
     AP_CHECK_PDL_LAUNCH("latent_decode_merge",
                         ap_launch_pdl(latent_decode_merge_kernel, dim3((unsigned)nseq, (unsigned)nh), dim3(128), 0, stream,
