@@ -207,8 +207,8 @@ def bench_latent_decode(args) -> dict:
 
 def bench_latent_prefill(args) -> dict:
     """One prompt on per-head keys and values ``[token][head][key | rotated part | value]`` (what the latent
-    mixer's product forms for prompt portions): the tensor-core kernel of ``ops.attention_window_bias`` with
-    pages of one token."""
+    mixer's product forms for prompt portions): ``ops.latent_prefill``, or with ``--general`` the tensor-core
+    kernel of ``ops.attention_window_bias`` with pages of one token."""
     from allpaca_b200 import ops
     T, nh, dk, dv = args.tokens, args.heads, args.head_dim + args.rot_dim, args.value_dim
     kv = torch.randn(T, nh, 1, dk + dv, device="cuda", dtype=torch.bfloat16)
@@ -220,12 +220,16 @@ def bench_latent_prefill(args) -> dict:
     pos = torch.arange(T, device="cuda", dtype=torch.int32)
 
     def fn(i):
-        ops.attention_window_bias(q, out, kv, where, start, pos, 1, nh, nh, dk, dv, 1.0 / math.sqrt(dk), 0, None, None,
-                                  single_rows=False, other_rows=True, bias=None, gate=gate, record=dk + dv,
-                                  value_offset=dk)
+        if args.general:
+            ops.attention_window_bias(q, out, kv, where, start, pos, 1, nh, nh, dk, dv, 1.0 / math.sqrt(dk), 0, None,
+                                      None, single_rows=False, other_rows=True, bias=None, gate=gate, record=dk + dv,
+                                      value_offset=dk)
+        else:
+            ops.latent_prefill(q, out, kv.view(T, nh * (dk + dv)), where, start, pos, 1, nh, dk, dv,
+                               1.0 / math.sqrt(dk), gate)
     us = _time(fn, args.iters, args.warmup, not args.no_graph)
     flops = 2.0 * nh * (dk + dv) * T * (T + 1) / 2
-    return {"kernel": "attention_window_bias_mma", "tokens": T, "heads": nh, "key_dim": dk, "value_dim": dv,
+    return {"kernel": "attention_window_bias_mma" if args.general else "latent_prefill", "tokens": T, "heads": nh, "key_dim": dk, "value_dim": dv,
             "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
@@ -459,6 +463,8 @@ def main(argv=None) -> int:
         s.add_argument("--batch", type=int, default=8)
         s.add_argument("--context", type=int, default=4096)
         s.add_argument("--tokens", type=int, default=2048)
+        s.add_argument("--general", action="store_true",
+                       help="latent-prefill: the general windowed kernel (pages of one token) instead of the one made for it")
     s = sub.add_parser("versus-reference")
     s.add_argument("--iters", type=int, default=20)
     s.add_argument("--warmup", type=int, default=3)

@@ -754,8 +754,8 @@ def check_kernel_status() -> None:
 
 
 from .mixers import (attention_window_bias, causal_conv_silu, embed_sinusoid_norm, gated_group_rmsnorm,  # noqa: E402
-                     head_project, latent_decode, latent_decode_takes, latent_gather, latent_prepare, qk_norm_store,
-                     ssm_scan)
+                     head_project, latent_decode, latent_decode_takes, latent_gather, latent_prefill,
+                     latent_prefill_takes, latent_prepare, qk_norm_store, ssm_scan)
 from . import routed  # noqa: E402,F401
 from .routed import (gated_act, moe_combine, moe_down, moe_gate_up, moe_gather, moe_max_tiles,  # noqa: E402
                      moe_route, moe_route_rows, moe_sort)

@@ -64,6 +64,10 @@ _CORE_SIGNATURES = {
     "ap_latent_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _L, _F, _P, _L, _I, _P, _L, _P],
     "ap_latent_decode_splits": [_I, _I, _I],
     "ap_latent_decode_takes": [_I, _I],
+    # int ap_latent_prefill(q, out, kv, where, width, seq_start, positions, nseq, T, nh, key, value, scale, gate,
+    #                       gate_ld, stream)
+    "ap_latent_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _L, _P],
+    "ap_latent_prefill_takes": [_I, _I],
     # int ap_causal_conv_silu(in, ld_in, col0, w, bias, state, state_stride, token_seq, seq_start, positions,
     #                         state_slots, out, T, nseq, C, taps, stream)
     "ap_causal_conv_silu": [_P, _L, _I, _P, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],

@@ -377,3 +377,37 @@ def latent_decode(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
     call(lib, "ap_latent_decode", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(), block_table.data_ptr(),
          block_table.shape[1], seq_start.data_ptr(), positions.data_ptr(), int(num_seqs), int(num_heads), int(record),
          int(value_dim), P, page_stride, float(scale), gptr, gld, nsplit, scratch.data_ptr(), need, stream_handle())
+
+
+def latent_prefill_takes(key_dim: int, value_dim: int) -> bool:
+    """Whether :func:`latent_prefill` takes these head sizes."""
+    return bool(core().ap_latent_prefill_takes(int(key_dim), int(value_dim)))
+
+
+def latent_prefill(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, where: torch.Tensor, seq_start: torch.Tensor,
+                   positions: torch.Tensor, num_seqs: int, num_heads: int, key_dim: int, value_dim: int, scale: float,
+                   gate: Optional[torch.Tensor] = None) -> None:
+    """bfloat16 causal attention of the sequences that bring SEVERAL rows on per-head keys and values
+    ``kv [tokens, heads*(key_dim + value_dim)]`` in which a sequence's tokens follow one another from row
+    ``where[s, 0]`` on (what :func:`latent_gather` and the product after it leave):
+    ``q [T, heads*key_dim]`` -> ``out [T, heads*value_dim]`` times ``sigmoid(gate[t, h])``; rows of sequences
+    that bring one row are left alone."""
+    _check(q, "q", torch.bfloat16, 2)
+    _check(out, "out", torch.bfloat16, 2)
+    _check(kv, "kv", torch.bfloat16, 2)
+    _check(where, "where", torch.int32, 2)
+    _check(seq_start, "seq_start", torch.int32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    T = q.shape[0]
+    if q.shape[1] != num_heads * key_dim or tuple(out.shape) != (T, num_heads * value_dim) \
+            or kv.shape[1] != num_heads * (key_dim + value_dim) or where.shape[0] < num_seqs:
+        raise KernelError("latent_prefill: shapes disagree")
+    gptr, gld = 0, 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.dim() != 2 or gate.shape[0] < T or gate.shape[1] != num_heads \
+                or gate.stride(1) != 1 or not gate.is_cuda:
+            raise KernelError("latent_prefill: the gate must be 32-bit [T, heads] with contiguous rows")
+        gptr, gld = gate.data_ptr(), gate.stride(0)
+    call(core(), "ap_latent_prefill", q.data_ptr(), out.data_ptr(), kv.data_ptr(), where.data_ptr(), where.shape[1],
+         seq_start.data_ptr(), positions.data_ptr(), int(num_seqs), T, int(num_heads), int(key_dim), int(value_dim),
+         float(scale), gptr, gld, stream_handle())

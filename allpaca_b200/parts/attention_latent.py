@@ -27,8 +27,9 @@ multiplications instead of ``head_dim + rot_dim``.  Where the latent is wide (a 
 numbers) the bfloat16 engine therefore serves sequences that bring several rows the other way round:
 the records of their tokens so far are gathered from the pages, ONE product with the matrix
 ``[W_uk[a] | 0; 0 | I; W_uv[a] | 0]`` stacked over the heads turns them into per-head
-``[key | rotated key part | value]`` rows, and the tensor-core attention kernel runs on those (to it, pages
-of one token with ``H`` key/value heads).  The identity block copies the rotated part exactly.
+``[key | rotated key part | value]`` rows, and a tensor-core attention kernel made for such rows runs on
+those (head sizes it does not take go to the general kernel, to which they are pages of one token with
+``H`` key/value heads).  The identity block copies the rotated part exactly.
 """
 from __future__ import annotations
 
@@ -176,8 +177,13 @@ class LatentAttention(Mixer):
             key = self.hd + self.rot
             qr = ws.get("lattn.qr", (T, self.nh * key), dt)
             ops.head_project(q, None, qr, self.nh, tail=self.rot, tail_dims=self.rot_dims, cos_sin=cos_sin)
-            ops.attention_window_bias(qr, ov, kv.view(total, self.nh, 1, key + self.vd), where, step.seq_start,
-                                      step.positions, step.num_seqs, self.nh, self.nh, key, self.vd, self.scale, 0,
-                                      None, None, single_rows="skip" if singles else False, other_rows=True, bias=None,
-                                      gate=gate, record=key + self.vd, value_offset=key)
+            if ops.latent_prefill_takes(key, self.vd):
+                ops.latent_prefill(qr, ov, kv, where, step.seq_start, step.positions, step.num_seqs, self.nh, key,
+                                   self.vd, self.scale, gate)
+            else:
+                # to the general tensor-core kernel these are pages of one token with a key/value head per head
+                ops.attention_window_bias(qr, ov, kv.view(total, self.nh, 1, key + self.vd), where, step.seq_start,
+                                          step.positions, step.num_seqs, self.nh, self.nh, key, self.vd, self.scale, 0,
+                                          None, None, single_rows="skip" if singles else False, other_rows=True,
+                                          bias=None, gate=gate, record=key + self.vd, value_offset=key)
         return self.o.forward(ov, "lattn.o", "delta")

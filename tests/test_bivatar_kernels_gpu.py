@@ -319,3 +319,53 @@ def test_single_rows_in_the_latent_space_on_the_tensor_cores(H, R, rot, P, max_c
             close(got[starts[s]], want[s], 2e-2, ("sequence of", lens[s]))
         else:
             assert torch.isnan(got[starts[s]:starts[s + 1]]).all(), "rows of a sequence that brings two were written"
+
+
+@pytest.mark.parametrize("H,DK,DV", [(3, 40, 40), (2, 192, 128), (5, 56, 8), (2, 96, 72), (1, 136, 64)])
+def test_prompt_rows_on_per_head_keys_and_values(H, DK, DV):
+    """Three sequences in one launch: 70 rows behind 130 earlier tokens, one row (left alone), and 129 rows
+    from position 0; per-head keys and values lie token after token.  Chosen rows look hard at one key: the
+    first of all, the first and last of a tile of 64, the row itself."""
+    from allpaca_b200 import ops
+    g = torch.Generator().manual_seed(H + DK)
+    lens = [(130, 70), (40, 1), (0, 129)]
+    scale = 1.0 / math.sqrt(DK)
+    kvs, qs, gates, want, positions, starts, where = [], [], [], [], [], [0], []
+    base = 0
+    for before, now in lens:
+        T = before + now
+        q = torch.randn(T, H, DK, generator=g)
+        k = torch.randn(T, H, DK, generator=g)
+        v = torch.randn(T, H, DV, generator=g)
+        gate = 2.0 * torch.randn(T, H, generator=g)
+        for row, key in {T - 1: 0, before: min(64, before), T - 2: 63, T - 3: T - 3, before + 1: before}.items():
+            if 0 <= key <= row < T and row >= before:
+                k[key] = 0.3 * k[key] + 6.0 * q[row] / q[row].norm(dim=-1, keepdim=True) * math.sqrt(DK)
+        q, k, v = (t.to(torch.bfloat16).double() for t in (q, k, v))
+        s = torch.einsum("ihd,jhd->hij", q, k) * scale
+        s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+        full = torch.einsum("hij,jhe->ihe", torch.softmax(s, dim=-1), v) * torch.sigmoid(gate.double())[:, :, None]
+        want.append(full[before:])
+        qs.append(q[before:])
+        gates.append(gate[before:])
+        positions += list(range(before, T))
+        starts.append(starts[-1] + now)
+        if now > 1:
+            kvs.append(torch.cat([k, v], dim=-1).reshape(T, H * (DK + DV)))
+            where.append(list(range(base, base + T)))
+            base += T
+        else:
+            where.append([])
+    width = max(len(w) for w in where)
+    wh = i32([w + [-1] * (width - len(w)) for w in where])
+    kv = torch.cat(kvs).to(torch.bfloat16).to(DEV).contiguous()
+    T = starts[-1]
+    q = torch.cat(qs).reshape(T, H * DK).to(torch.bfloat16).to(DEV).contiguous()
+    gate = torch.cat(gates).to(DEV).contiguous()
+    out = torch.full((T, H * DV), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert ops.latent_prefill_takes(DK, DV)
+    ops.latent_prefill(q, out, kv, wh, i32(starts), i32(positions), len(lens), H, DK, DV, scale, gate)
+    got = out.float().cpu().view(T, H, DV)
+    close(got[:70], want[0], 2e-2, "rows behind earlier tokens")
+    close(got[71:], want[2], 2e-2, "rows from position 0")
+    assert torch.isnan(got[70]).all(), "the row of a sequence that brings one was written"
