@@ -174,7 +174,7 @@ AP_EXPORT int ap_add_rmsnorm(float* x, const float* delta, int S, long long delt
 // absent).  Without partial sums (S = 0) only the copy is made.  One CTA per row; the sum of
 // squares and the addition are 32-bit.
 // ---------------------------------------------------------------------------
-template <typename TW, typename TO>
+template <typename TW, typename TO, int VEC>
 __global__ void norm_residual_kernel(float* __restrict__ x, const float* __restrict__ delta, int S, size_t delta_stride,
                                      const TW* __restrict__ w, float eps, float mult, TO* __restrict__ copy, int H) {
     extern __shared__ __align__(16) float row_buf[];
@@ -183,25 +183,51 @@ __global__ void norm_residual_kernel(float* __restrict__ x, const float* __restr
     ap_pdl_trigger();
     ap_pdl_wait();
     float* xr = x + (size_t)t * H;
+    TO* cr = copy ? copy + (size_t)t * H : nullptr;
     if (S == 0) {
-        if (copy)
-            for (int i = threadIdx.x; i < H; i += blockDim.x) copy[(size_t)t * H + i] = ap_from_float<TO>(xr[i]);
+        if (cr)
+            for (int i = threadIdx.x; i < H; i += blockDim.x) cr[i] = ap_from_float<TO>(xr[i]);
         return;
     }
     const float* dr = delta + (size_t)t * H;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = dr[i];
-        for (int s = 1; s < S; ++s) v += dr[(size_t)s * delta_stride + i];
-        row_buf[i] = v;
-        ss = fmaf(v, v, ss);
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+        float v[VEC];
+        if (VEC == 4) {
+            const float4 a = *reinterpret_cast<const float4*>(dr + i);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+            for (int s = 1; s < S; ++s) {
+                const float4 d = *reinterpret_cast<const float4*>(dr + (size_t)s * delta_stride + i);
+                v[0] += d.x; v[1] += d.y; v[2] += d.z; v[3] += d.w;
+            }
+        } else {
+            v[0] = dr[i];
+            for (int s = 1; s < S; ++s) v[0] += dr[(size_t)s * delta_stride + i];
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            row_buf[i + e] = v[e];
+            ss = fmaf(v[e], v[e], ss);
+        }
     }
     ss = ap_block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = xr[i] + mult * (row_buf[i] * inv * ap_to_float(w[i]));
-        xr[i] = v;
-        if (copy) copy[(size_t)t * H + i] = ap_from_float<TO>(v);
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+        float v[VEC];
+        if (VEC == 4) {
+            const float4 a = *reinterpret_cast<const float4*>(xr + i);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        } else {
+            v[0] = xr[i];
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) v[e] += mult * (row_buf[i + e] * inv * ap_to_float(w[i + e]));
+        if (VEC == 4) *reinterpret_cast<float4*>(xr + i) = make_float4(v[0], v[1], v[2], v[3]);
+        else xr[i] = v[0];
+        if (cr) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) cr[i + e] = ap_from_float<TO>(v[e]);
+        }
     }
 }
 
@@ -213,11 +239,15 @@ AP_EXPORT int ap_norm_residual(float* x, const float* delta, int S, long long de
     if (T == 0 || (S == 0 && copy == nullptr)) return AP_OK;
     const size_t smem = (size_t)H * sizeof(float);
     AP_REQUIRE(smem <= 200 * 1024, "norm_residual: width %d does not fit the shared-memory row buffer", H);
-    int threads = (H + 31) / 32 * 32;
+    // whole rows of four 32-bit numbers where the addresses allow; many rows: smaller blocks, several rows to an SM
+    const bool vec = (H % 4 == 0) && (((uintptr_t)x & 15) == 0) && (S == 0 || ((((uintptr_t)delta & 15) == 0) && (delta_stride % 4 == 0)));
+    const int per = vec ? 4 : 1;
+    int threads = ((H + per - 1) / per + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
+    if (T >= 4 * 148 && threads > 256) threads = 256;
 #define LAUNCH(TW, TO)                                                                                                 \
     do {                                                                                                               \
-        auto kern = norm_residual_kernel<TW, TO>;                                                                      \
+        auto kern = vec ? norm_residual_kernel<TW, TO, 4> : norm_residual_kernel<TW, TO, 1>;                           \
         if (smem > 48 * 1024) {                                                                                        \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
             AP_REQUIRE(e == cudaSuccess, "norm_residual: cannot reserve %zu bytes of shared memory", smem);            \

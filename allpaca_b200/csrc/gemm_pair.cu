@@ -93,7 +93,7 @@ template <typename TO, bool PAIRS>
 __global__ void __launch_bounds__(192)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                     TO* __restrict__ out, int M, int N, int K, long long ldc, int tiles_m, int tiles_total, int bn,
-                    int split, int shared, int* __restrict__ flags, float* __restrict__ partials) {
+                    int split, int shared, int* __restrict__ flags, float* __restrict__ partials, int act) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* w_tiles = smem;
@@ -407,7 +407,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_con
                         const float up = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? v[16 + jj] : other)));
                         const int col = c + (odd ? 16 : 0) + jj;
                         if (col < cols && n < N)
-                            dst[(size_t)jj * ldc] = ap_from_float<TO>(__fdividef(gt, 1.0f + __expf(-gt)) * up);
+                            {
+                            // act 1: the tanh form of GELU, tanh(z) = 1 - 2 / (exp(2z) + 1); else silu
+                            float gv;
+                            if (act == 1) {
+                                const float z = 0.7978845608028654f * (gt + 0.044715f * gt * gt * gt);
+                                gv = 0.5f * gt * (2.0f - __fdividef(2.0f, __expf(2.0f * z) + 1.0f));
+                            } else {
+                                gv = __fdividef(gt, 1.0f + __expf(-gt));
+                            }
+                            dst[(size_t)jj * ldc] = ap_from_float<TO>(gv * up);
+                        }
                     }
                 } else if (n < N) {
 #pragma unroll
@@ -470,7 +480,7 @@ static bool pair_make_map(CUtensorMap* map, const void* base, long long rows, lo
 
 template <typename TO, bool PAIRS>
 static int launch_pair(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N, int K, long long ldc,
-                       int bn, int tiles_m, void* scratch, long long scratch_bytes, cudaStream_t stream) {
+                       int bn, int tiles_m, void* scratch, long long scratch_bytes, int act, cudaStream_t stream) {
     auto kern = gemm_tc_pair_kernel<TO, PAIRS>;
     static bool configured = false;
     static int sms = 0;
@@ -537,7 +547,7 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& ma, void* out, 
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
     cfg.numAttrs = ap_pdl_enabled() ? 2 : 1;
     AP_CHECK_PDL_LAUNCH("gemm_tc_pair", cudaLaunchKernelEx(&cfg, kern, mw, ma, (TO*)out, M, N, K, ldc, tiles_m,
-                                                           (int)tiles, bn, split, shared, flags, partials));
+                                                           (int)tiles, bn, split, shared, flags, partials, act));
     return AP_OK;
 }
 
@@ -559,6 +569,8 @@ AP_EXPORT int ap_gemm_tc_pair(const void* a, const void* w, void* out, int out_d
                "gemm_tc_pair: K=%d and the leading dimensions must be multiples of 8 (16-byte rows for TMA)", K);
     AP_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc_pair: operands must be 16-byte aligned");
     AP_REQUIRE(!pairs || N % 2 == 0, "gemm_tc_pair: gate and up rows alternate, so the weight has an even number of rows");
+    AP_REQUIRE(pairs >= 0 && pairs <= 2, "gemm_tc_pair: pairs is 0, 1 (silu) or 2 (gelu_tanh)");
+    const int act = pairs == 2 ? 1 : 0;
     AP_REQUIRE(lda >= K && ldw >= K && ldc >= (pairs ? N / 2 : N), "gemm_tc_pair: a leading dimension is below its row length");
     AP_REQUIRE(out_dtype == AP_F32 || out_dtype == AP_BF16, "gemm_tc_pair: unknown output dtype %d", out_dtype);
     // token tiles of at most 256 rows, evenly filled; a tile's width is a multiple of 32 (each CTA
@@ -570,12 +582,12 @@ AP_EXPORT int ap_gemm_tc_pair(const void* a, const void* w, void* out, int out_d
     AP_REQUIRE(pair_make_map(&ma, a, M, K, lda, bn / 2), "gemm_tc_pair: cannot encode the activations' tensor map");
     if (pairs) {
         return out_dtype == AP_F32
-                   ? launch_pair<float, true>(mw, ma, out, M, N, K, ldc, bn, tiles_m, scratch, scratch_bytes, stream)
-                   : launch_pair<bf16, true>(mw, ma, out, M, N, K, ldc, bn, tiles_m, scratch, scratch_bytes, stream);
+                   ? launch_pair<float, true>(mw, ma, out, M, N, K, ldc, bn, tiles_m, scratch, scratch_bytes, act, stream)
+                   : launch_pair<bf16, true>(mw, ma, out, M, N, K, ldc, bn, tiles_m, scratch, scratch_bytes, act, stream);
     }
     return out_dtype == AP_F32
-               ? launch_pair<float, false>(mw, ma, out, M, N, K, ldc, bn, tiles_m, scratch, scratch_bytes, stream)
-               : launch_pair<bf16, false>(mw, ma, out, M, N, K, ldc, bn, tiles_m, scratch, scratch_bytes, stream);
+               ? launch_pair<float, false>(mw, ma, out, M, N, K, ldc, bn, tiles_m, scratch, scratch_bytes, 0, stream)
+               : launch_pair<bf16, false>(mw, ma, out, M, N, K, ldc, bn, tiles_m, scratch, scratch_bytes, 0, stream);
 }
 
 // Whether this kernel is the one to use for a product of many rows.  Measured against the

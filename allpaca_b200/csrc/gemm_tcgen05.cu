@@ -82,6 +82,7 @@ struct EpiArgs {
     long long ldxb;
     float* ss_out;           // EPI_RESIDUAL: [M][ss_out_parts]
     int ss_out_parts;
+    int act;                 // EPI_PAIRS: the gate's activation (see gated())
     // EPI_ROPE
     bf16* q_out;             // [M][nh * hd]
     bf16* cache;             // one layer's pages [page][2][nkv][P][hd], or nullptr: store no K, V
@@ -123,7 +124,16 @@ __device__ __forceinline__ void rope_store_pair(const EpiArgs& ea, int m, int n,
     dst[ib] = __float2bfloat16_rn(b);
 }
 
-__device__ __forceinline__ float gated(float gate, float up) { return __fdividef(gate, 1.0f + __expf(-gate)) * up; }
+// The gated activation of a feed-forward in a product's epilogue: act 0: silu(gate) * up; 1: the tanh
+// form of GELU, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * up, with tanh(z) = 1 - 2 / (exp(2z) + 1).
+__device__ __forceinline__ float gated(float gate, float up, int act) {
+    if (act == 1) {
+        const float z = 0.7978845608028654f * (gate + 0.044715f * gate * gate * gate);
+        const float th = 1.0f - __fdividef(2.0f, __expf(2.0f * z) + 1.0f);
+        return 0.5f * gate * (1.0f + th) * up;
+    }
+    return __fdividef(gate, 1.0f + __expf(-gate)) * up;
+}
 // the four epilogue warps among themselves (barrier 1; barrier 0 is __syncthreads)
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -349,7 +359,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         const float gt = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? other : v[j]) * sc));
                         const float up = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? v[8 + j] : other) * sc));
                         const int m = m0 + col;
-                        if (m < M && n < N) out[(size_t)m * ldc + (n >> 1)] = ap_from_float<TO>(gated(gt, up));
+                        if (m < M && n < N) out[(size_t)m * ldc + (n >> 1)] = ap_from_float<TO>(gated(gt, up, ea.act));
                     }
                 } else if (EPI == EPI_ROPE) {
                     // even lane: row n, odd lane: row n + 1 of a pair; the even lane finishes token
@@ -451,7 +461,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     gt = ap_to_float(ap_from_float<TO>(gt * inv_s[c]));
                     up = ap_to_float(ap_from_float<TO>(up * inv_s[c]));
                     const int n = n0 + first + 2 * i;
-                    if (n < N) out[(size_t)(m0 + c) * ldc + (n >> 1)] = ap_from_float<TO>(gated(gt, up));
+                    if (n < N) out[(size_t)(m0 + c) * ldc + (n >> 1)] = ap_from_float<TO>(gated(gt, up, ea.act));
                 }
             } else if (EPI == EPI_ROPE) {
                 const int prs = rows / 2;
@@ -816,7 +826,10 @@ AP_EXPORT int ap_gemm_tc(const void* a, const void* w, void* out, int out_dtype,
     AP_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0,
                "gemm_tc: K=%d and the leading dimensions must be multiples of 8 (16-byte rows for TMA)", K);
     AP_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
-    AP_REQUIRE(epi == EPI_PLAIN || epi == EPI_PAIRS || epi == EPI_RESIDUAL, "gemm_tc: unknown epilogue %d", epi);
+    // EPI_PAIRS: the gate's activation rides above the code (gemm_tc_run takes the two apart)
+    AP_REQUIRE((epi & 0xff) == EPI_PLAIN || (epi & 0xff) == EPI_PAIRS || (epi & 0xff) == EPI_RESIDUAL,
+               "gemm_tc: unknown epilogue %d", epi & 0xff);
+    AP_REQUIRE((epi >> 8) == 0 || ((epi >> 8) == 1 && (epi & 0xff) == EPI_PAIRS), "gemm_tc: unknown activation %d", epi >> 8);
     return gemm_tc_run(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, reduce, epi, ss_in,
                        ss_in_parts, inv_width, eps, xb, ldxb, ss_out, ss_out_parts, nullptr, stream);
 }
@@ -826,6 +839,8 @@ static int gemm_tc_run(const void* a, const void* w, void* out, int out_dtype, i
                        int reduce, int epi, const float* ss_in, int ss_in_parts, float inv_width, float eps,
                        void* xb, long long ldxb, float* ss_out, int ss_out_parts, const EpiArgs* rope,
                        cudaStream_t stream) {
+    const int act = epi >> 8;                               // the gate's activation of EPI_PAIRS
+    epi &= 0xff;
     const bool pairs = epi == EPI_PAIRS;
     AP_REQUIRE(lda >= K && ldw >= K && ldc >= (pairs ? N / 2 : N), "gemm_tc: a leading dimension is below its row length");
     const int kb_total = (K + TILE_K - 1) / TILE_K;
@@ -848,6 +863,7 @@ static int gemm_tc_run(const void* a, const void* w, void* out, int out_dtype, i
     EpiArgs ea = {};
     if (rope) ea = *rope;
     ea.ss_in = ss_in; ea.ss_in_parts = ss_in_parts; ea.inv_width = inv_width; ea.eps = eps;
+    ea.act = act;
     if (epi == EPI_RESIDUAL) {
         AP_REQUIRE(out_dtype == AP_F32 && M <= 256 && (nsplit == 1 || (cluster && (nsplit == 2 || nsplit == 4 || nsplit == 8))),
                    "gemm_tc: the residual epilogue adds into a 32-bit matrix of at most 256 rows, with 1, 2, 4 or 8 "
@@ -1046,7 +1062,7 @@ template <int BN, typename TO, bool PAIRS>
 __global__ void __launch_bounds__(192)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a,
                           TO* __restrict__ out, int M, int N, int K, long long ldc, int tiles_m, int tiles_total,
-                          int bn, int split, int* __restrict__ flags, float* __restrict__ partials) {
+                          int bn, int split, int* __restrict__ flags, float* __restrict__ partials, int act) {
     using Cfg = PersistCfg<BN>;
     constexpr int STAGES = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -1267,7 +1283,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
                         const float up = ap_to_float(ap_from_float<TO>(__uint_as_float(odd ? v[16 + jj] : other)));
                         const int col = c + (odd ? 16 : 0) + jj;
                         if (col < cols && n < N)
-                            dst[(size_t)jj * ldc] = ap_from_float<TO>(__fdividef(gt, 1.0f + __expf(-gt)) * up);
+                            dst[(size_t)jj * ldc] = ap_from_float<TO>(gated(gt, up, act));
                     }
                 } else if (n < N) {
 #pragma unroll
@@ -1291,7 +1307,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __gr
 
 template <int BN, typename TO, bool PAIRS>
 static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& ma, void* out, int M, int N, int K,
-                             long long ldc, int bn, void* scratch, long long scratch_bytes, cudaStream_t stream) {
+                             long long ldc, int bn, void* scratch, long long scratch_bytes, int act,
+                             cudaStream_t stream) {
     using Cfg = PersistCfg<BN>;
     auto kern = gemm_tc_persistent_kernel<BN, TO, PAIRS>;
     static bool configured = false;
@@ -1334,7 +1351,7 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& ma, void*
     dim3 grid((unsigned)ctas, 1, 1);
     AP_CHECK_PDL_LAUNCH("gemm_tc_persistent", ap_launch_pdl(kern, grid, dim3(192), (size_t)Cfg::kSmemBytes, stream, mw,
                                                             ma, (TO*)out, M, N, K, ldc, tiles_m, (int)tiles, bn,
-                                                            split, flags, partials));
+                                                            split, flags, partials, act));
     return AP_OK;
 }
 
@@ -1347,7 +1364,8 @@ AP_EXPORT long long ap_gemm_tc_persistent_scratch_bytes(void) {
 
 // The persistent kernel (see gemm_tc_persistent_kernel), for products with more than 64 rows.
 //   pairs == 0: out[M, N] = a * w^T for w [N, K].
-//   pairs != 0: w [N, K] has gate and up rows alternating; out[M, N/2] = silu(gate) * up.
+//   pairs != 0: w [N, K] has gate and up rows alternating; out[M, N/2] = silu(gate) * up (pairs 1) or
+//               gelu_tanh(gate) * up (pairs 2).
 //   scratch: null, or ap_gemm_tc_persistent_scratch_bytes() bytes (see there).
 AP_EXPORT int ap_gemm_tc_persistent(const void* a, const void* w, void* out, int out_dtype, int M, int N, int K,
                                     long long lda, long long ldw, long long ldc, int pairs, void* scratch,
@@ -1358,6 +1376,8 @@ AP_EXPORT int ap_gemm_tc_persistent(const void* a, const void* w, void* out, int
                "gemm_tc: K=%d and the leading dimensions must be multiples of 8 (16-byte rows for TMA)", K);
     AP_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
     AP_REQUIRE(!pairs || N % 2 == 0, "gemm_tc: gate and up rows alternate, so the weight has an even number of rows");
+    AP_REQUIRE(pairs >= 0 && pairs <= 2, "gemm_tc: pairs is 0, 1 (silu) or 2 (gelu_tanh)");
+    const int act = pairs == 2 ? 1 : 0;
     AP_REQUIRE(lda >= K && ldw >= K && ldc >= (pairs ? N / 2 : N), "gemm_tc: a leading dimension is below its row length");
     AP_REQUIRE(out_dtype == AP_F32 || out_dtype == AP_BF16, "gemm_tc: unknown output dtype %d", out_dtype);
     // token tiles: as many as tiles of the full width (128 for up to 128 rows, else 256) would
@@ -1392,8 +1412,8 @@ AP_EXPORT int ap_gemm_tc_persistent(const void* a, const void* w, void* out, int
     AP_REQUIRE(make_map(&ma, a, M, K, lda, bn), "gemm_tc: cannot encode the activations' tensor map");
 #define GO(BN, PR)                                                                                                  \
     return out_dtype == AP_F32                                                                                      \
-               ? launch_persistent<BN, float, PR>(mw, ma, out, M, N, K, ldc, bn, scratch, scratch_bytes, stream)    \
-               : launch_persistent<BN, bf16, PR>(mw, ma, out, M, N, K, ldc, bn, scratch, scratch_bytes, stream)
+               ? launch_persistent<BN, float, PR>(mw, ma, out, M, N, K, ldc, bn, scratch, scratch_bytes, act, stream) \
+               : launch_persistent<BN, bf16, PR>(mw, ma, out, M, N, K, ldc, bn, scratch, scratch_bytes, act, stream)
     if (pairs) {
         if (cap == 128) GO(128, true);
         GO(256, true);

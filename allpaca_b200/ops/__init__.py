@@ -49,6 +49,18 @@ def _partials(t: torch.Tensor, name: str):
     raise KernelError(f"{name} must be [T,N] or [S,T,N], has shape {tuple(t.shape)}")
 
 
+def _pairs_code(pairs) -> int:
+    """What the products take as ``pairs``: False/None: no gated epilogue; True or ``"silu"``:
+    ``silu(gate) * up``; ``"gelu_tanh"``: the tanh form of GELU on the gate."""
+    if not pairs:
+        return 0
+    if pairs is True or pairs == "silu":
+        return 1
+    if pairs == "gelu_tanh":
+        return 2
+    raise KernelError(f"the gated epilogue of a product knows silu and gelu_tanh, not {pairs!r}")
+
+
 def embed_gather(tokens: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: float = 1.0) -> None:
     """``x[t] = table[tokens[t]] * scale`` into the 32-bit residual stream ``x [T,H]``."""
     _check(tokens, "tokens", torch.int32, 1)
@@ -311,7 +323,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, nsplit: int = 1
         stride = M * N
     ss, parts, inv_width, eps = _scale_args(scale, M)
     call(core(), "ap_gemm_tc", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
-         M, N, K, K, K, N // 2 if pairs else N, nsplit, stride, 1 if reduce else 0, 1 if pairs else 0,
+         M, N, K, K, K, N // 2 if pairs else N, nsplit, stride, 1 if reduce else 0,
+         (1 | ((_pairs_code(pairs) - 1) << 8)) if pairs else 0,
          ss, parts, inv_width, eps, 0, 0, 0, 0, stream_handle())
 
 
@@ -414,7 +427,7 @@ def gemm_tc_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pairs: boo
         raise KernelError(f"gemm_tc_pair: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     scratch = _scratch_for_persistent(a.device) if share_tiles else None
     call(core(), "ap_gemm_tc_pair", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
-         M, N, K, K, K, n_out, 1 if pairs else 0, scratch.data_ptr() if scratch is not None else 0,
+         M, N, K, K, K, n_out, _pairs_code(pairs), scratch.data_ptr() if scratch is not None else 0,
          scratch.numel() if scratch is not None else 0, stream_handle())
 
 
@@ -455,7 +468,7 @@ def gemm_tc_persistent(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, pair
                           f"out {tuple(out.shape)}")
     scratch = _scratch_for_persistent(a.device) if share_tiles else None
     call(core(), "ap_gemm_tc_persistent", a.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
-         M, N, K, K, K, n_out, 1 if pairs else 0, scratch.data_ptr() if scratch is not None else 0,
+         M, N, K, K, K, n_out, _pairs_code(pairs), scratch.data_ptr() if scratch is not None else 0,
          scratch.numel() if scratch is not None else 0, stream_handle())
 
 

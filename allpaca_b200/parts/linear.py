@@ -130,10 +130,11 @@ class Linear:
             return True
         return False
 
-    def forward_gated(self, a: torch.Tensor, buffer_name: str, scale=None) -> Optional[torch.Tensor]:
-        """For a weight whose rows alternate gate and up: ``silu(a W_gate^T) * (a W_up^T)`` in one
-        kernel, ``[T, out/2]`` in the activation type; None when the shape is not one the fused
-        kernel is used for (the caller then multiplies and activates separately)."""
+    def forward_gated(self, a: torch.Tensor, buffer_name: str, scale=None, activation: str = "silu") -> Optional[torch.Tensor]:
+        """For a weight whose rows alternate gate and up: ``act(a W_gate^T) * (a W_up^T)`` in one
+        kernel (``activation``: ``"silu"`` or ``"gelu_tanh"``), ``[T, out/2]`` in the activation type; None
+        when the shape is not one the fused kernel is used for (the caller then multiplies and activates
+        separately)."""
         T = a.shape[0]
         if not self.uses_tensor_cores() or self.out_features % 2 or self.bias is not None:
             return None
@@ -143,9 +144,9 @@ class Linear:
             if scale is not None:
                 raise ValueError("a scale of the rows is only applied by the tensor-core kernel for few rows")
             if ops.gemm_tc_prefers_pair(T, self.out_features, self.in_features):
-                ops.gemm_tc_pair(a, self.weight, out, pairs=True)
+                ops.gemm_tc_pair(a, self.weight, out, pairs=activation)
             else:
-                ops.gemm_tc_persistent(a, self.weight, out, pairs=True)
+                ops.gemm_tc_persistent(a, self.weight, out, pairs=activation)
         else:
-            ops.gemm_tc(a, self.weight, out, nsplit, reduce=nsplit > 1, pairs=True, scale=scale)
+            ops.gemm_tc(a, self.weight, out, nsplit, reduce=nsplit > 1, pairs=activation, scale=scale)
         return out

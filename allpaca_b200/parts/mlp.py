@@ -21,8 +21,9 @@ from .linear import Linear
 @register("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
     """Parameters: ``hidden_size``, ``intermediate_size``, ``bias`` (False: no biases, as on the
-    Llama path), ``activation`` of the gate (``"silu"``, or ``"relu"``: then the activation is a
-    kernel of its own after the product, and the norm before is not folded in), ``names`` (the
+    Llama path), ``activation`` of the gate (``"silu"`` and ``"gelu_tanh"`` are applied in the
+    product's epilogue on the tensor cores; others, like ``"relu"``, by a kernel of its own after the
+    product; only with ``"silu"`` is the norm before folded in), ``names`` (the
     local tensor names of gate, up and down; default ``gate_proj.weight`` and so on)."""
 
     def __init__(self, params, env: BuildEnv):
@@ -75,14 +76,14 @@ class SwiGLU(FeedForward):
 
     def forward(self, h: torch.Tensor, step) -> torch.Tensor:
         T = h.shape[0]
-        if self.activation != "silu":
-            gu = self.gate_up.forward(h, "ffn.gate_up", "either")
-            act = self.env.workspace.get("ffn.act", (T, self.inter), self.env.dtype)
-            ops.gated_act(gu, act, self.activation, pairs=True)
-            return self.down.forward(act, "ffn.down", "delta")
-        act = self.gate_up.forward_gated(h, "ffn.act")        # one kernel when there are many rows
+        act = None
+        if self.activation in ("silu", "gelu_tanh"):
+            act = self.gate_up.forward_gated(h, "ffn.act", activation=self.activation)   # the product's epilogue
         if act is None:
             gu = self.gate_up.forward(h, "ffn.gate_up", "either")
             act = self.env.workspace.get("ffn.act", (T, self.inter), self.env.dtype)
-            ops.swiglu(gu, act, pairs=True)
+            if self.activation == "silu":
+                ops.swiglu(gu, act, pairs=True)
+            else:
+                ops.gated_act(gu, act, self.activation, pairs=True)
         return self.down.forward(act, "ffn.down", "delta")

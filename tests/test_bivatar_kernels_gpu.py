@@ -369,3 +369,27 @@ def test_prompt_rows_on_per_head_keys_and_values(H, DK, DV):
     close(got[:70], want[0], 2e-2, "rows behind earlier tokens")
     close(got[71:], want[2], 2e-2, "rows from position 0")
     assert torch.isnan(got[70]).all(), "the row of a sequence that brings one was written"
+
+
+@pytest.mark.parametrize("M", [3, 16, 100, 300, 2048])
+def test_feed_forward_gate_in_the_products_epilogue(M):
+    """The gate-and-up product with the tanh form of GELU applied in its epilogue (few rows, many rows on one SM
+    and on a pair of SMs), against the product and the gate computed apart."""
+    from allpaca_b200 import ops
+    from allpaca_b200.parts import BuildEnv, Workspace
+    from allpaca_b200.parts.linear import Linear
+    g = torch.Generator().manual_seed(M)
+    K, I = 256, 1024
+    env = BuildEnv(dtype=torch.bfloat16, device=torch.device(DEV), workspace=Workspace(torch.device(DEV)))
+    gate = (torch.randn(I, K, generator=g) * 0.1).to(torch.bfloat16)
+    up = (torch.randn(I, K, generator=g) * 0.1).to(torch.bfloat16)
+    lin = Linear(env, 2 * I, K)
+    lin.load(torch.stack([gate, up], dim=1).reshape(2 * I, K).to(DEV))
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    got = lin.forward_gated(a.to(DEV), "t.act", activation="gelu_tanh")
+    assert got is not None
+    # the gate and the up value pass through the storage type before the activation
+    gt = (a.double() @ gate.double().T).to(torch.bfloat16).double()
+    u = (a.double() @ up.double().T).to(torch.bfloat16).double()
+    close(got.float(), plain.gelu_tanh(gt) * u, 1e-2, "gated product")
+    ops.check_kernel_status()
