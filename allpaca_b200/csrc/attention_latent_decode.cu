@@ -10,8 +10,10 @@
 //   O [16 x R] += P [16 x 64] V [64 x R]          warp w: its eighth of the R columns; V is the same
 //                                                 tile, read transposed (ldmatrix.trans)
 //
-// Key tiles come by cp.async into two buffers, the next one loading while this one is used.  The
-// slices of a sequence's keys leave unnormalised sums with their maximum and weight sum; a second
+// Key tiles come by cp.async.  With one tile buffer (LD_STAGES 1, the default) two CTAs share an SM and
+// one computes while the other loads; with two buffers a CTA loads its next tile while it uses this
+// one and has the SM alone (measured: 74 against 110 us for 64 sequences of 2048 keys, 32 against 34
+// for 8 of 4096, 39 against 34 for one of 8192).  The slices of a sequence's keys leave unnormalised sums with their maximum and weight sum; a second
 // kernel merges them, applies the output gate and rounds.  Scores, softmax and sums are 32-bit.
 #include "common.cuh"
 #include <float.h>
@@ -21,6 +23,9 @@
 #define LD_KT 64              // keys per tile: eight to a warp
 #define LD_M 16               // heads per CTA
 #define LD_PP 72              // row pitch of the probabilities in shared memory (64 + 8)
+#ifndef LD_STAGES
+#define LD_STAGES 1           // key tile buffers per CTA: with one, two CTAs share an SM and overlap each other's loads
+#endif
 
 __device__ __forceinline__ void ld_cp_async16(void* smem, const void* gmem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -66,8 +71,8 @@ latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
     const int D16 = (D + 15) & ~15;
     const int pitch = D16 + 8;                               // 16 bytes more than a row: ldmatrix meets no bank twice
     bf16* q_s = reinterpret_cast<bf16*>(ld_smem);            // [16][pitch]
-    bf16* k_s = q_s + LD_M * pitch;                          // [2][64][pitch]
-    bf16* p_s = k_s + 2 * LD_KT * pitch;                     // [16][LD_PP]
+    bf16* k_s = q_s + LD_M * pitch;                          // [LD_STAGES][64][pitch]
+    bf16* p_s = k_s + LD_STAGES * LD_KT * pitch;             // [16][LD_PP]
     float* red = reinterpret_cast<float*>(p_s + LD_M * LD_PP);   // [LD_WARPS][16]
     const int* table = block_table + (size_t)seq * max_blocks;
     const int tiles = qpos / LD_KT + 1;
@@ -107,13 +112,14 @@ latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
 #pragma unroll
     for (int i = 0; i < NBW; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-FLT_MAX, -FLT_MAX}, l[2] = {0.f, 0.f};
-    if (t0 < t1) load_tile(t0, 0);
+    if (LD_STAGES == 2 && t0 < t1) load_tile(t0, 0);
     for (int tile = t0; tile < t1; ++tile) {
-        const int stage = (tile - t0) & 1;
-        if (tile + 1 < t1) {
+        const int stage = LD_STAGES == 2 ? (tile - t0) & 1 : 0;
+        if (LD_STAGES == 2 && tile + 1 < t1) {
             load_tile(tile + 1, stage ^ 1);
             ld_cp_async_wait<1>();
         } else {
+            if (LD_STAGES == 1) load_tile(tile, 0);
             ld_cp_async_wait<0>();
         }
         __syncthreads();                                     // the tile (and, the first time, the queries) are there
@@ -285,7 +291,8 @@ latent_decode_merge_kernel(const float* __restrict__ part_o, const float* __rest
 AP_EXPORT int ap_latent_decode_splits(int nseq, int nh, int max_context) {
     const int groups = (nh + LD_M - 1) / LD_M;
     const int tiles = (max_context > 0 ? max_context : 1) / LD_KT + 1;
-    int want = (148 + nseq * groups - 1) / (nseq * groups > 0 ? nseq * groups : 1);
+    const int slots = 148 * (LD_STAGES == 1 ? 2 : 1);          // CTAs the GPU holds at once
+    int want = (slots + nseq * groups - 1) / (nseq * groups > 0 ? nseq * groups : 1);
     const int most = tiles / 2 > 0 ? tiles / 2 : 1;
     if (want > most) want = most;
     if (want > 32) want = 32;                                // the merge adds them up one after another
@@ -295,7 +302,7 @@ AP_EXPORT int ap_latent_decode_splits(int nseq, int nh, int max_context) {
 // Whether the kernel takes these sizes (else the caller uses the general kernels).
 AP_EXPORT int ap_latent_decode_takes(int D, int R) {
     const int D16 = (D + 15) & ~15;
-    const size_t smem = (size_t)(LD_M + 2 * LD_KT) * (D16 + 8) * 2 + LD_M * LD_PP * 2 + LD_WARPS * LD_M * 4;
+    const size_t smem = (size_t)(LD_M + LD_STAGES * LD_KT) * (D16 + 8) * 2 + LD_M * LD_PP * 2 + LD_WARPS * LD_M * 4;
     return D > 0 && R > 0 && D % 8 == 0 && R % 8 == 0 && R <= D && R <= 512 && smem <= 220 * 1024;
 }
 
@@ -314,7 +321,7 @@ AP_EXPORT int ap_latent_decode(const void* q, void* out, const void* cache, cons
     const int groups = (nh + LD_M - 1) / LD_M;
     AP_REQUIRE(groups <= 65535 && nsplit <= 65535, "latent_decode: the grid is too large");
     const int D16 = (D + 15) & ~15;
-    const size_t smem = (size_t)(LD_M + 2 * LD_KT) * (D16 + 8) * 2 + LD_M * LD_PP * 2 + LD_WARPS * LD_M * 4;
+    const size_t smem = (size_t)(LD_M + LD_STAGES * LD_KT) * (D16 + 8) * 2 + LD_M * LD_PP * 2 + LD_WARPS * LD_M * 4;
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)nseq * nsplit * nh * R;
     const dim3 grid((unsigned)nseq, (unsigned)groups, (unsigned)nsplit);
