@@ -99,3 +99,22 @@ def test_window_release_keeps_the_first_pages():
     m.free("r")
     m.check()
     assert m.num_free_pages(1) == 40
+
+
+def test_random_model_folder_from_the_command_line(tmp_path):
+    """``allpaca init-random --config`` writes a Bivatar folder the engine's reader accepts: every tensor the
+    description names and no other (a layer that reads another's latent has no down-projection to it)."""
+    import json
+    from allpaca_b200 import cli
+    from allpaca_b200.models import load_config
+    from allpaca_b200.weights.safetensors_io import Checkpoint
+    src = tmp_path / "config.json"
+    src.write_text(json.dumps(CONFIGS["A"]))
+    assert cli.main(["init-random", "--config", str(src), "--seed", "3", "--out", str(tmp_path / "m"),
+                     "--dtype", "bfloat16"]) == 0
+    arch, cfg = load_config(str(tmp_path / "m"))
+    assert arch.name == "Bivatar" and cfg.torch_dtype == "bfloat16" and len(cfg.layers) == 6
+    ckpt = Checkpoint(str(tmp_path / "m"))
+    shapes = plain_bivatar.tensor_shapes(CONFIGS["A"])
+    assert set(ckpt.names()) == set(shapes)
+    assert "l2.mix.dkv" not in shapes and tuple(ckpt.tensor("l3.mix.dkv").shape) == (48, 64)
