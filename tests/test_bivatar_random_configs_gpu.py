@@ -1,0 +1,113 @@
+"""Bivatar configurations drawn at random (layer order, head counts and sizes, latents that are and are
+not multiples of 8, windows and kept first tokens, latents shared over several layers, page sizes)
+through the engine in 32-bit and in bfloat16 against the plain implementation: the whole prompt in
+one step, then portions beside another request's decoding, then the last tokens one by one."""
+import random
+
+import numpy as np
+import pytest
+
+import helpers
+import plain_bivatar
+from test_bivatar_engine_gpu import write_folder
+
+pytestmark = pytest.mark.gpu
+# 32-bit: three times what rounding alone does to this configuration (the plain implementation in 32-bit against itself
+# in 64-bit; deep stacks with a sharp softmax carry rounding far), at least 2e-5 of the largest logit.  bfloat16: the
+# root mean square of a row's deviations against that of the logits; rounding has a long tail, so no row over three
+# times the tolerance and at most one row in ten over it; the tolerance grows (up to threefold) with what the
+# configuration does to 32-bit rounding.
+FLOOR32 = 2e-5
+TOL16 = 3e-2
+
+
+def draw(seed):
+    rnd = random.Random(seed)
+    width = rnd.choice([8 * rnd.randrange(6, 40), 8 * rnd.randrange(6, 40), rnd.randrange(40, 200)])
+    layers, latents = [], []
+    for i in range(rnd.choice([2, 3, 4, 5, 7])):
+        mlp = {"kind": "dense", "ff": rnd.choice([8 * rnd.randrange(6, 50), rnd.randrange(30, 200)])} \
+            if rnd.random() < 0.8 else None
+        if rnd.random() < 0.6:
+            heads = rnd.choice([1, 2, 3, 4, 6, 8, 12, 17])
+            src = rnd.choice(latents) if latents and rnd.random() < 0.5 else None
+            if src is None:
+                rot_dim = rnd.choice([2, 4, 8, 16, 32, 64])
+                kv_rank = rnd.choice([8 * rnd.randrange(2, 12), 8 * rnd.randrange(12, 40), rnd.randrange(10, 150)])
+                scaling = None
+                if rnd.random() < 0.7:
+                    scaling = {"factor": rnd.choice([2.0, 8.0, 40.0]), "original": rnd.choice([16, 64, 2048]),
+                               "fast": rnd.choice([4.0, 32.0]), "slow": rnd.choice([0.5, 1.0])}
+                rot = {"dims": rot_dim, "base": rnd.choice([100.0, 10000.0, 50000.0]), "scaling": scaling}
+                latents.append(i)
+            else:
+                m = layers[src]["mixer"]
+                rot_dim, kv_rank, rot = m["rot_dim"], m["kv_rank"], m["rot"]
+            dim = rnd.choice([8, 16, 24, 32, 64, 20, 128])
+            mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": rnd.choice([8, 16, 40, 64, 80, 128, 12]),
+                     "kv_rank": kv_rank, "q_rank": rnd.choice([8 * rnd.randrange(2, 30), rnd.randrange(10, 100)]),
+                     "scale": round((dim + rot_dim) ** -0.5 * rnd.choice([1.0, 2.0]), 4), "rot": rot}
+            if src is not None:
+                mixer["kv_from"] = src
+            layers.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+        else:
+            kv = rnd.choice([1, 2, 3, 4])
+            dim = rnd.choice([8, 16, 32, 48, 64, 128, 20])
+            mixer = {"heads": kv * rnd.choice([1, 2, 3, 4, 8]), "kv_heads": kv, "dim": dim,
+                     "vdim": rnd.choice([8, 16, 32, 64, 128, 12, 160]), "scale": round(dim ** -0.5 * rnd.choice([1.0, 2.0]), 4)}
+            if rnd.random() < 0.8:
+                mixer["mask"] = {"size": rnd.choice([1, 3, 16, 31, 64, 100]), "keep_first": rnd.choice([0, 1, 4, 17, 40])}
+            layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    config = {"architecture": "Bivatar", "vocab": rnd.choice([130, 257, 300, 511]), "width": width,
+              "norm": {"eps": rnd.choice([1e-5, 1e-6])}, "residual_mult": rnd.choice([0.25, 0.5, 1.0, 1.3]),
+              "embedding": {"scale": rnd.choice([0.5, 1.0, 3.0])}, "layers": layers}
+    return config, rnd.choice([4, 8, 16, 32, 64]), rnd.choice([70, 150, 333])
+
+
+@pytest.mark.parametrize("seed", [3, 11, 29, 42, 57, 68, 71, 90, 101, 113])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_configuration(tmp_path, seed, dtype):
+    from allpaca_b200 import ops
+    from allpaca_b200.config import EngineConfig
+    from allpaca_b200.engine.batch import BatchEntry
+    from allpaca_b200.engine.runner import ModelRunner
+    config, page, n = draw(seed)
+    weights = write_folder(tmp_path / "m", config, seed, dtype)
+    toks = helpers.random_tokens(n, config["vocab"], seed)
+    plain = plain_bivatar.forward(config, weights, toks).numpy()
+    import torch
+    rounding = np.abs(plain_bivatar.forward(config, weights, toks, dtype=torch.float32).numpy() - plain).max()
+    rounding /= np.abs(plain).max()
+    tol = max(FLOOR32, 3.0 * rounding)
+    # a configuration that carries 32-bit rounding further than usual (2e-5) carries bfloat16 rounding further too
+    tol16 = TOL16 * min(3.0, max(1.0, rounding / 2e-5))
+    runner = ModelRunner(str(tmp_path / "m"), EngineConfig(dtype=dtype, page_size=page, max_cache_tokens=2048,
+                                                           max_num_seqs=4, max_num_batched_tokens=512))
+    errors = []
+
+    def judge(got, rows, what):
+        want = plain[rows]
+        assert np.isfinite(got).all(), (config, what)
+        if dtype == "float32":
+            e = np.abs(got - want).max() / np.abs(plain).max()
+            assert e < tol, (config, what, float(e), tol)
+        else:
+            errors.extend((np.sqrt(((got - want) ** 2).mean(axis=-1)) / np.sqrt((plain ** 2).mean())).tolist())
+    want = sorted({0, 1, n // 2, n - 2, n - 1})
+    judge(runner.step([BatchEntry("w", toks, want)]).double().cpu().numpy(), want, "whole")
+    runner.finish("w")
+    at = 0
+    runner.step([BatchEntry("o", toks[:9], [])])
+    for k, c in enumerate([n // 3, 2, n - 20 - n // 3 - 2]):
+        out = runner.step([BatchEntry("o", toks[9 + k:10 + k], [0]), BatchEntry("p", toks[at:at + c], [c - 1])])
+        out = out.double().cpu().numpy()
+        judge(out[:1], [9 + k], ("the decoding request", k))
+        judge(out[1:], [at + c - 1], ("portion", at, c))
+        at += c
+    while at < n:
+        judge(runner.step([BatchEntry("p", toks[at:at + 1], [0])]).double().cpu().numpy(), [at], ("decoded", at))
+        at += 1
+    ops.check_kernel_status()
+    if dtype == "bfloat16":
+        assert max(errors) <= 3 * tol16, (config, page, n, max(errors))
+        assert sum(e > tol16 for e in errors) <= max(1, len(errors) // 10), (config, page, n, sorted(errors)[-5:])
