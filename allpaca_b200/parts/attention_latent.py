@@ -145,6 +145,8 @@ class LatentAttention(Mixer):
         q = self.uq.forward(cq, "lattn.q", "float32")
         rec = self.R + self.rot
         gate = proj[:, self.Q + self.kv_size:] if self.output_gate else None
+        # The host's lists decide only between steps that differ in kind: a step of single rows only (what a CUDA
+        # graph records, and every replay is again such a step) never reads them beyond this line
         lens = step.host_query_lens
         singles = step.max_query_len == 1 or 1 in lens
         per_head = self.expands and step.max_query_len > 1
